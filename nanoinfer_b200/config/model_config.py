@@ -103,6 +103,11 @@ class ModelConfig:
     def from_json_dict(cls, d: Mapping[str, Any]) -> "ModelConfig":
         raise NotImplementedError
 
+    def with_tensor_shapes(self, shapes: Mapping[str, Any]) -> "ModelConfig":
+        """This configuration with the sizes filled in that config.json leaves to the checkpoint (``shapes``: tensor
+        name -> shape). Most architectures state every size in config.json and return themselves."""
+        return self
+
 
 @dataclass(frozen=True)
 class Qwen2Config(ModelConfig):

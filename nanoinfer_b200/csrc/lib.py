@@ -80,7 +80,9 @@ class Kernels:
                      "nib_attention_decode_tma_supported",
                      "nib_attention_decode_tma_error", "nib_argmax", "nib_argmax_chunked", "nib_sample", "nib_repetition_penalty", "nib_device_arch",
                      "nib_sm_count", "nib_gemm_smallm_qkv", "nib_gemm_smallm_qkv_supported", "nib_gemm_tc_qkv",
-                     "nib_gemm_tc_qkv_supported"):
+                     "nib_gemm_tc_qkv_supported", "nib_poly_norm", "nib_depth_mix", "nib_unary", "nib_head_norm_gate",
+                     "nib_delta_rule_scan", "nib_causal_conv", "nib_rglru_scan", "nib_latent_store", "nib_latent_query",
+                     "nib_latent_attention", "nib_latent_value"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -551,6 +553,147 @@ class Kernels:
             return _cluster_splits(n)
         most = max(1, (8 * self.sm_count) // max(1, n_tokens * kv_heads))
         return max(1, min(-(-tiles // 2), most, 64))
+
+    # ---- row-wise and element-wise kernels that several designs share (pointwise.cu) -------------
+    @staticmethod
+    def _rows(t, dtype, what):
+        """A matrix whose rows are dense but may lie apart (a slice of the columns of a wider one)."""
+        _need(t, dtype, what, contiguous=False)
+        if t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"{what}: rows must be dense")
+
+    def poly_norm(self, z32, coef32, eps, out):
+        """out = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 per row, N(y) = y / sqrt(mean(y^2) + eps); coef32 = (c0..c3)."""
+        self._rows(z32, torch.float32, "poly_norm z"); self._rows(out, None, "poly_norm out")
+        _need(coef32, torch.float32, "poly_norm coefficients")
+        if z32.shape != out.shape or coef32.numel() != 4:
+            raise KernelError("poly_norm: shapes do not fit")
+        self._check(self._lib.nib_poly_norm(_ptr(z32), c_int(z32.stride(0)), _ptr(coef32), _ptr(out), c_int(out.stride(0)),
+                                            c_int(z32.shape[0]), c_int(z32.shape[1]), c_float(eps), c_int(_DT[out.dtype]),
+                                            self._stream()), "poly_norm")
+
+    def depth_mix(self, hist32, x32, coef32, n):
+        """hist32[n-1] = x32, then x32 = sum_{j<n} coef32[j] * hist32[j] (ascending j)."""
+        _need(hist32, torch.float32, "depth_mix history"); _need(x32, torch.float32, "depth_mix x"); _need(coef32, torch.float32, "depth_mix coefficients")
+        if hist32.shape[0] < n or tuple(hist32.shape[1:]) != tuple(x32.shape) or coef32.numel() < n:
+            raise KernelError("depth_mix: shapes do not fit")
+        self._check(self._lib.nib_depth_mix(_ptr(hist32), _ptr(x32), _ptr(coef32), c_int(n), c_longlong(x32.numel()),
+                                            self._stream()), "depth_mix")
+
+    def unary(self, in32, out, kind):
+        """out = f(in32) element by element with a change of storage type; kind: 'tanh' | 'copy' | 'sigmoid'."""
+        self._rows(in32, torch.float32, "unary in"); self._rows(out, None, "unary out")
+        if in32.shape != out.shape:
+            raise KernelError("unary: shapes differ")
+        self._check(self._lib.nib_unary(_ptr(in32), c_int(in32.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(in32.shape[0]),
+                                        c_int(in32.shape[1]), c_int({"tanh": 0, "copy": 1, "sigmoid": 2}[kind]),
+                                        c_int(_DT[out.dtype]), self._stream()), "unary")
+
+    def head_norm_gate(self, o32, gate32, gain32, eps, heads, d, out):
+        """out[t, h, :] = o32[t, h, :] / rms(o32[t, h, :]) * gain32[h, :] * sigmoid(gate32[t, h, :])."""
+        self._rows(o32, torch.float32, "head_norm_gate o"); self._rows(gate32, torch.float32, "head_norm_gate gate")
+        self._rows(out, None, "head_norm_gate out"); _need(gain32, torch.float32, "head_norm_gate gain")
+        m = o32.shape[0]
+        if o32.shape[1] != heads * d or tuple(gate32.shape) != (m, heads * d) or tuple(out.shape) != (m, heads * d) or gain32.numel() != heads * d:
+            raise KernelError("head_norm_gate: shapes do not fit")
+        self._check(self._lib.nib_head_norm_gate(_ptr(o32), c_int(o32.stride(0)), _ptr(gate32), c_int(gate32.stride(0)), _ptr(gain32),
+                                                 _ptr(out), c_int(out.stride(0)), c_int(m), c_int(heads), c_int(d), c_float(eps),
+                                                 c_int(_DT[out.dtype]), self._stream()), "head_norm_gate")
+
+    # ---- recurrent mixers (recurrent.cu) -------------------------------------------------------------
+    def delta_rule_scan(self, r32, k32, v32, a_logit32, w_logit32, state, ctx, o32, heads, d):
+        """The generalized delta rule over every request's tokens in order, from and into ``state[slot]``
+        ([slots, heads, d (value channel), d (key channel)] floats). r32, k32, v32, a_logit32 are column slices of one
+        matrix (equal row strides); o32[t, h, :] = S_t^T r_t."""
+        for t, what in ((r32, "r"), (k32, "k"), (v32, "v"), (a_logit32, "a"), (w_logit32, "w"), (o32, "o")):
+            self._rows(t, torch.float32, f"delta_rule_scan {what}")
+        _need(state, torch.float32, "delta_rule_scan state")
+        m = r32.shape[0]
+        if any(tuple(t.shape) != (m, heads * d) for t in (r32, k32, v32, a_logit32, w_logit32, o32)) \
+                or len({t.stride(0) for t in (r32, k32, v32, a_logit32)}) != 1 or tuple(state.shape[1:]) != (heads, d, d):
+            raise KernelError("delta_rule_scan: shapes do not fit")
+        self._check(self._lib.nib_delta_rule_scan(
+            _ptr(r32), _ptr(k32), _ptr(v32), _ptr(a_logit32), c_int(r32.stride(0)), _ptr(w_logit32), c_int(w_logit32.stride(0)),
+            _ptr(state), _ptr(ctx.q_start), _ptr(ctx.state_slots), _ptr(o32), c_int(o32.stride(0)), c_int(ctx.host.num_requests),
+            c_int(heads), c_int(d), self._stream()), "delta_rule_scan")
+
+    def causal_conv(self, x32, w32, bias32, state, hist_row0, ctx, u32, u_blocks, taps, blocks):
+        """u = bias + sum_j w[:, j] * x[t - (taps-1-j)] per channel within each request; inputs before the step's first
+        token come from ``state[slot, hist_row0 : hist_row0 + taps - 1]``. u32: [tokens, width] floats; u_blocks:
+        the same values as [blocks, tokens, width / blocks] in the storage type."""
+        self._rows(x32, torch.float32, "causal_conv x"); _need(w32, torch.float32, "causal_conv w"); _need(bias32, torch.float32, "causal_conv bias")
+        _need(state, torch.float32, "causal_conv state"); _need(u32, torch.float32, "causal_conv u32"); _need(u_blocks, None, "causal_conv u_blocks")
+        m, width = x32.shape
+        if tuple(w32.shape) != (width, taps) or state.shape[2] != width or hist_row0 + taps - 1 > state.shape[1] \
+                or tuple(u32.shape) != (m, width) or tuple(u_blocks.shape) != (blocks, m, width // blocks):
+            raise KernelError("causal_conv: shapes do not fit")
+        self._check(self._lib.nib_causal_conv(
+            _ptr(x32), c_int(x32.stride(0)), _ptr(w32), _ptr(bias32), _ptr(state), c_int(state.shape[1]), c_int(hist_row0),
+            _ptr(ctx.q_start), _ptr(ctx.req_index), _ptr(ctx.state_slots), _ptr(u32), _ptr(u_blocks), c_int(m), c_int(width),
+            c_int(taps), c_int(blocks), c_int(_DT[u_blocks.dtype]), self._stream()), "causal_conv")
+
+    def rglru_scan(self, u32, gates32, y_logit32, x32, softplus_lam32, state, ctx, out, taps, blocks):
+        """S <- a S + sqrt(1 - a^2) (i * u), a = exp(-8 r softplus(lam)), r | i = sigmoid of a block's gate logits
+        (gates32: [blocks, tokens, 2 * width / blocks]); out = S * gelu_tanh(y_logit32). ``state[slot, 0]`` is S;
+        rows 1.. become the request's last taps-1 rows of x32."""
+        _need(u32, torch.float32, "rglru_scan u"); _need(gates32, torch.float32, "rglru_scan gates"); self._rows(y_logit32, torch.float32, "rglru_scan y")
+        self._rows(x32, torch.float32, "rglru_scan x"); _need(softplus_lam32, torch.float32, "rglru_scan lam"); _need(state, torch.float32, "rglru_scan state")
+        _need(out, None, "rglru_scan out")
+        m, width = u32.shape
+        if tuple(gates32.shape) != (blocks, m, 2 * (width // blocks)) or tuple(state.shape[1:]) != (taps, width) \
+                or tuple(out.shape) != (m, width) or tuple(y_logit32.shape) != (m, width) or tuple(x32.shape) != (m, width):
+            raise KernelError("rglru_scan: shapes do not fit")
+        self._check(self._lib.nib_rglru_scan(
+            _ptr(u32), _ptr(gates32), _ptr(y_logit32), c_int(y_logit32.stride(0)), _ptr(x32), c_int(x32.stride(0)),
+            _ptr(softplus_lam32), _ptr(state), _ptr(ctx.q_start), _ptr(ctx.state_slots), _ptr(out), c_int(m),
+            c_int(ctx.host.num_requests), c_int(width), c_int(taps), c_int(blocks), c_int(_DT[out.dtype]), self._stream()), "rglru_scan")
+
+    # ---- attention through a latent (latent_attention.cu) -------------------------------------------
+    def latent_store(self, z32, gain32, eps, freq32, mag, ctx, block_table, page_size, pages, rank, rot):
+        """Cache rows [rms-normed z[:, :rank] * gain | z[:, rank:] rotated in interleaved pairs by position * freq32]."""
+        self._rows(z32, torch.float32, "latent_store z"); _need(gain32, torch.float32, "latent_store gain"); _need(freq32, torch.float32, "latent_store freq")
+        _need(pages, None, "latent_store pages"); _need(block_table, torch.int32, "block_table", contiguous=False)
+        if z32.shape[1] != rank + rot or tuple(pages.shape[1:]) != (1, page_size, rank + rot) or freq32.numel() != rot // 2 \
+                or block_table.stride(1) != 1:
+            raise KernelError("latent_store: shapes do not fit")
+        self._check(self._lib.nib_latent_store(
+            _ptr(z32), c_int(z32.stride(0)), _ptr(gain32), c_float(eps), _ptr(freq32), c_float(mag), _ptr(ctx.positions),
+            _ptr(ctx.req_index), _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), _ptr(pages),
+            c_int(pages.shape[0]), c_int(z32.shape[0]), c_int(rank), c_int(rot), c_int(_DT[pages.dtype]), self._stream()), "latent_store")
+
+    def latent_query(self, q32, w_uk, freq32, mag, positions, qa32, heads, dn, rank, rot):
+        """qa32[t, h] = [W_uk,h^T q32[t, h, :dn] | q32[t, h, dn:] rotated]; w_uk: [heads * dn, rank] as stored."""
+        self._rows(q32, torch.float32, "latent_query q"); _need(w_uk, None, "latent_query w_uk"); _need(qa32, torch.float32, "latent_query qa")
+        _need(freq32, torch.float32, "latent_query freq")
+        m = q32.shape[0]
+        if q32.shape[1] != heads * (dn + rot) or tuple(w_uk.shape) != (heads * dn, rank) or tuple(qa32.shape) != (m, heads * (rank + rot)):
+            raise KernelError("latent_query: shapes do not fit")
+        self._check(self._lib.nib_latent_query(_ptr(q32), c_int(q32.stride(0)), _ptr(w_uk), _ptr(freq32), c_float(mag), _ptr(positions),
+                                               _ptr(qa32), c_int(m), c_int(heads), c_int(dn), c_int(rank), c_int(rot),
+                                               c_int(_DT[w_uk.dtype]), self._stream()), "latent_query")
+
+    def latent_attention(self, qa32, lat32, ctx, block_table, page_size, pages, heads, rank, rot, scale, window):
+        """lat32[t, h] = sum_j softmax_j((qa32[t, h] . row_j) * scale) * row_j[:rank] over the cached rows of the token's
+        request at positions lo..own (lo = own - window + 1 with a window)."""
+        _need(qa32, torch.float32, "latent_attention qa"); _need(lat32, torch.float32, "latent_attention out"); _need(pages, None, "latent_attention pages")
+        _need(block_table, torch.int32, "block_table", contiguous=False)
+        m = qa32.shape[0]
+        if tuple(qa32.shape) != (m, heads * (rank + rot)) or tuple(lat32.shape) != (m, heads * rank) \
+                or tuple(pages.shape[1:]) != (1, page_size, rank + rot) or block_table.stride(1) != 1:
+            raise KernelError("latent_attention: shapes do not fit")
+        self._check(self._lib.nib_latent_attention(
+            _ptr(qa32), _ptr(lat32), _ptr(ctx.positions), _ptr(ctx.req_index), _ptr(block_table), c_int(block_table.stride(0)),
+            c_int(page_size), _ptr(pages), c_int(pages.shape[0]), c_int(m), c_int(heads), c_int(rank), c_int(rot), c_float(scale),
+            c_int(window), c_int(_DT[pages.dtype]), self._stream()), "latent_attention")
+
+    def latent_value(self, lat32, w_uv, out, heads, dv, rank):
+        """out[t, h*dv + j] = w_uv[h*dv + j, :] . lat32[t, h, :]."""
+        _need(lat32, torch.float32, "latent_value lat"); _need(w_uv, None, "latent_value w_uv"); self._rows(out, w_uv.dtype, "latent_value out")
+        m = lat32.shape[0]
+        if tuple(lat32.shape) != (m, heads * rank) or tuple(w_uv.shape) != (heads * dv, rank) or tuple(out.shape) != (m, heads * dv):
+            raise KernelError("latent_value: shapes do not fit")
+        self._check(self._lib.nib_latent_value(_ptr(lat32), _ptr(w_uv), _ptr(out), c_int(out.stride(0)), c_int(m), c_int(heads),
+                                               c_int(dv), c_int(rank), c_int(_DT[w_uv.dtype]), self._stream()), "latent_value")
 
     def argmax(self, logits, out):
         """First index of each row's maximum. Few rows of a large vocabulary are cut into pieces for many CTAs."""

@@ -1,0 +1,139 @@
+// Row-wise and element-wise kernels that several designs share: the PolyNorm activation (a mix of the
+// rms-normed first three powers of a row), the weighted sum of a step's earlier residual streams, a
+// unary function with a change of storage type, and the norm-and-gate of a recurrent mixer's heads.
+// All arithmetic is 32-bit; T is the storage type of the activations that leave (float or bfloat16).
+#include "common.cuh"
+
+__device__ __forceinline__ float block_sum_256(float v, float* part) {
+    // fixed order: warp butterflies, then the eight warps' sums added ascending by every thread
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += part[w];
+    __syncthreads();
+    return t;
+}
+
+// ---------------------------------------------------------------------------------- PolyNorm
+// out[t, :] = c0 z / rms(z) + c1 z^2 / rms(z^2) + c2 z^3 / rms(z^3) + c3, rms(y) = sqrt(mean(y^2) + eps).
+// One block of 256 threads per row; the row is read twice (sums of z^2, z^4, z^6; then the result).
+template <typename T>
+__global__ void __launch_bounds__(256)
+poly_norm_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ coef, T* __restrict__ out, int ldo,
+                 int width, float eps) {
+    __shared__ float part[8];
+    const float* zr = z + (size_t)blockIdx.x * ldz;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int c = threadIdx.x; c < width; c += 256) {
+        const float v = zr[c], v2 = v * v, v3 = v2 * v;
+        s2 = fmaf(v, v, s2);
+        s4 = fmaf(v2, v2, s4);
+        s6 = fmaf(v3, v3, s6);
+    }
+    s2 = block_sum_256(s2, part);
+    s4 = block_sum_256(s4, part);
+    s6 = block_sum_256(s6, part);
+    const float inv = 1.0f / (float)width;
+    const float n1 = coef[0] / sqrtf(s2 * inv + eps), n2 = coef[1] / sqrtf(s4 * inv + eps), n3 = coef[2] / sqrtf(s6 * inv + eps);
+    const float c3 = coef[3];
+    T* o = out + (size_t)blockIdx.x * ldo;
+    for (int c = threadIdx.x; c < width; c += 256) {
+        const float v = zr[c], v2 = v * v;
+        Elem<T>::store(o + c, fmaf(n1, v, fmaf(n2, v2, fmaf(n3, v2 * v, c3))));
+    }
+}
+
+NIB_API int nib_poly_norm(const float* z, int ldz, const float* coef, void* out, int ldo, int rows, int width, float eps,
+                          int dtype, cudaStream_t stream) {
+    NIB_REQUIRE(rows >= 0 && width > 0 && ldz >= width && ldo >= width, "poly_norm: bad sizes rows=%d width=%d", rows, width);
+    if (rows == 0) return 0;
+    if (dtype == NIB_F32) poly_norm_kernel<float><<<rows, 256, 0, stream>>>(z, ldz, coef, (float*)out, ldo, width, eps);
+    else if (dtype == NIB_BF16) poly_norm_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>(z, ldz, coef, (__nv_bfloat16*)out, ldo, width, eps);
+    else NIB_REQUIRE(false, "poly_norm: unknown dtype %d", dtype);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------- weighted sum of streams
+// hist holds `cap` streams of `n_elem` floats each. The newest stream is x (it becomes hist[n - 1]); x then
+// becomes sum_{j < n} coef[j] * hist[j], added in ascending j.
+__global__ void depth_mix_kernel(float* __restrict__ hist, float* __restrict__ x, const float* __restrict__ coef, int n,
+                                 long long n_elem) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_elem) return;
+    const float newest = x[i];
+    hist[(size_t)(n - 1) * n_elem + i] = newest;
+    float acc = 0.f;
+    for (int j = 0; j < n - 1; ++j) acc = fmaf(coef[j], hist[(size_t)j * n_elem + i], acc);
+    x[i] = fmaf(coef[n - 1], newest, acc);
+}
+
+NIB_API int nib_depth_mix(float* hist, float* x, const float* coef, int n, long long n_elem, cudaStream_t stream) {
+    NIB_REQUIRE(n >= 1 && n_elem >= 0, "depth_mix: bad sizes n=%d", n);
+    if (n_elem == 0) return 0;
+    depth_mix_kernel<<<ceil_div(n_elem, 256), 256, 0, stream>>>(hist, x, coef, n, n_elem);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------- unary function + cast
+// out[t, c] = f(in[t, c]) for c < width; kind 0: tanh, 1: identity, 2: sigmoid.
+template <typename T>
+__global__ void unary_kernel(const float* __restrict__ in, int ld_in, T* __restrict__ out, int ld_out, int rows, int width, int kind) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * width) return;
+    const int t = (int)(i / width), c = (int)(i % width);
+    float v = in[(size_t)t * ld_in + c];
+    if (kind == 0) v = tanhf(v);
+    else if (kind == 2) v = 1.0f / (1.0f + expf(-v));
+    Elem<T>::store(out + (size_t)t * ld_out + c, v);
+}
+
+NIB_API int nib_unary(const float* in, int ld_in, void* out, int ld_out, int rows, int width, int kind, int dtype,
+                      cudaStream_t stream) {
+    NIB_REQUIRE(rows >= 0 && width > 0 && kind >= 0 && kind <= 2, "unary: bad arguments");
+    if (rows == 0) return 0;
+    const int blocks = ceil_div((long long)rows * width, 256);
+    if (dtype == NIB_F32) unary_kernel<float><<<blocks, 256, 0, stream>>>(in, ld_in, (float*)out, ld_out, rows, width, kind);
+    else if (dtype == NIB_BF16) unary_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(in, ld_in, (__nv_bfloat16*)out, ld_out, rows, width, kind);
+    else NIB_REQUIRE(false, "unary: unknown dtype %d", dtype);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------- per-head norm and gate
+// out[t, h*d + j] = o[t, h, j] / sqrt(mean_j o[t, h, :]^2 + eps) * gain[h*d + j] * sigmoid(gate[t, h*d + j]).
+// One warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ gate, int ldg,
+                      const float* __restrict__ gain, T* __restrict__ out, int ld_out, int tokens, int heads, int d, float eps) {
+    const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (w >= (long long)tokens * heads) return;
+    const int t = (int)(w / heads), h = (int)(w % heads);
+    const float* orow = o + (size_t)t * ldo + (size_t)h * d;
+    float ss = 0.f;
+    for (int j = lane; j < d; j += 32) ss = fmaf(orow[j], orow[j], ss);
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int j = lane; j < d; j += 32) {
+        const float g = gate[(size_t)t * ldg + (size_t)h * d + j];
+        const float v = orow[j] * scale * gain[h * d + j] * (1.0f / (1.0f + expf(-g)));
+        Elem<T>::store(out + (size_t)t * ld_out + (size_t)h * d + j, v);
+    }
+}
+
+NIB_API int nib_head_norm_gate(const float* o, int ldo, const float* gate, int ldg, const float* gain, void* out, int ld_out,
+                               int tokens, int heads, int d, float eps, int dtype, cudaStream_t stream) {
+    NIB_REQUIRE(tokens >= 0 && heads > 0 && d > 0, "head_norm_gate: bad sizes");
+    if (tokens == 0) return 0;
+    const int blocks = ceil_div((long long)tokens * heads, 4);
+    if (dtype == NIB_F32) head_norm_gate_kernel<float><<<blocks, 128, 0, stream>>>(o, ldo, gate, ldg, gain, (float*)out, ld_out, tokens, heads, d, eps);
+    else if (dtype == NIB_BF16) head_norm_gate_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(o, ldo, gate, ldg, gain, (__nv_bfloat16*)out, ld_out, tokens, heads, d, eps);
+    else NIB_REQUIRE(false, "head_norm_gate: unknown dtype %d", dtype);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}

@@ -24,7 +24,7 @@ from ..config.model_config import ModelConfig, read_config_json
 from ..models.decoder import DecoderModel
 from ..parts.base import HostBatch, Runtime, StepContext
 from ..registry import config_from_json_dict, plan_for
-from ..weights.loader import load_tensors
+from ..weights.loader import load_tensors, tensor_shapes
 
 _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -39,7 +39,7 @@ class StepEntry:
 class Engine:
     def __init__(self, model_dir: str, engine_config: EngineConfig, ops=None):
         self.engine_config = engine_config
-        self.config: ModelConfig = config_from_json_dict(read_config_json(model_dir))
+        self.config: ModelConfig = config_from_json_dict(read_config_json(model_dir)).with_tensor_shapes(tensor_shapes(model_dir))
         self.plan = plan_for(self.config)
         tensors = load_tensors(model_dir, self.plan)
         if ops is None:

@@ -117,6 +117,7 @@ class StepContext:
     block_tables: Dict[int, torch.Tensor] = field(default_factory=dict)  # cache group -> [R, pages]
     rt: Optional[Runtime] = None
     all_rows_wanted: bool = False  # logits are wanted at every row, in row order
+    scratch: Dict[str, object] = field(default_factory=dict)  # what parts of one step hand to later parts of the same step
 
 
 @dataclass

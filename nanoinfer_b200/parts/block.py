@@ -1,5 +1,8 @@
 """Arrangements: the order in which the parts of one layer run.
 
+``parallel``: ``x += mixer(norm_a(x)) + feed_forward(norm_b(x))``, both of the same x, optionally followed by a mix
+with the step's earlier streams.
+
 ``pre_norm``: ``x += mixer(norm(x)); x += feed_forward(norm(x))`` with a norm of its own before each
 (cpp/src/model.cpp:364-400, nanoinfer/layers.py:328-339). The residual stream ``x`` is 32-bit and
 both sums are made in 32-bit inside the projections that produce the addends.
@@ -29,4 +32,31 @@ class PreNormBlock:
         self.ffn.forward(normed_input(self.ffn_norm, self.ffn, x32), x32, ctx)
 
 
+class ParallelBlock:
+    """``x <- x + mixer(norm_a(x)) + feed_forward(norm_b(x))``: both branches read the same x. parts: ``mixer_norm``,
+    ``mixer``; optionally ``ffn_norm`` and ``ffn`` (a layer without a feed-forward), and ``depth`` (a part with
+    ``begin(x32, ctx)`` before and ``forward(x32, ctx)`` after the layer: what goes on is a mix of this and earlier
+    results). Both norms are computed before either branch adds to the stream."""
+
+    def __init__(self, parts: Dict[str, object]):
+        self.mixer_norm, self.mixer = parts["mixer_norm"], parts["mixer"]
+        self.ffn_norm, self.ffn = parts.get("ffn_norm"), parts.get("ffn")
+        self.depth = parts.get("depth")
+        if (self.ffn is None) != (self.ffn_norm is None):
+            raise ValueError("a parallel block has a feed-forward and its norm, or neither")
+        self.part_names = tuple(n for n in ("mixer_norm", "mixer", "ffn_norm", "ffn", "depth") if parts.get(n) is not None)
+
+    def forward(self, x32: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
+        h_mixer = self.mixer_norm.forward(x32)
+        h_ffn = self.ffn_norm.forward(x32) if self.ffn is not None else None
+        if self.depth is not None:
+            self.depth.begin(x32, ctx)
+        self.mixer.forward(h_mixer, x32, ctx, cache)
+        if self.ffn is not None:
+            self.ffn.forward(h_ffn, x32, ctx)
+        if self.depth is not None:
+            self.depth.forward(x32, ctx)
+
+
 register_arrangement("pre_norm", PreNormBlock)
+register_arrangement("parallel", ParallelBlock)

@@ -43,4 +43,39 @@ class SwiGLU(FeedForward):
         self.ops.linear(act, self.w_down, None, residual32, "add")
 
 
+class PolyNormFeedForward(FeedForward):
+    """``down(act(up(h)))`` with biases and ``act(z) = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3``: powers element by
+    element, ``N`` divides a token's vector by its root mean square (``eps`` inside the root), in 32-bit.
+    params: ``hidden``, ``intermediate``, ``eps``. tensors: ``up_w [intermediate, hidden]``, ``up_b``,
+    ``down_w [hidden, intermediate]``, ``down_b``, ``coef [4]``."""
+
+    graph_safe = True   # launches do not depend on which requests are in the batch
+
+    @staticmethod
+    def spec(prefix: str, hidden: int, intermediate: int, eps: float) -> PartSpec:
+        return PartSpec("polynorm_ffn", {"hidden": hidden, "intermediate": intermediate, "eps": eps}, {
+            "up_w": TensorSpec(f"{prefix}.up", (intermediate, hidden)),
+            "up_b": TensorSpec(f"{prefix}.up.b", (intermediate,), "bias"),
+            "down_w": TensorSpec(f"{prefix}.down", (hidden, intermediate)),
+            "down_b": TensorSpec(f"{prefix}.down.b", (hidden,), "bias"),
+            "coef": TensorSpec(f"{prefix}.act", (4,), "unit"),
+        })
+
+    def __init__(self, spec: PartSpec, tensors: Dict[str, torch.Tensor], rt: Runtime):
+        super().__init__(spec, tensors, rt)
+        self.hidden, self.intermediate = int(spec.params["hidden"]), int(spec.params["intermediate"])
+        self.eps = float(spec.params["eps"])
+        self.w_up, self.b_up = rt.matrix(tensors["up_w"]), rt.vector32(tensors["up_b"])
+        self.w_down, self.b_down = rt.matrix(tensors["down_w"]), rt.vector32(tensors["down_b"])
+        self.coef = rt.vector32(tensors["coef"])
+
+    def forward(self, h: torch.Tensor, residual32: torch.Tensor, ctx: StepContext) -> None:
+        z32 = torch.empty((h.shape[0], self.intermediate), dtype=torch.float32, device=h.device)
+        self.ops.linear(h, self.w_up, self.b_up, z32, "f32")
+        act = torch.empty((h.shape[0], self.intermediate), dtype=self.rt.dtype, device=h.device)
+        self.ops.poly_norm(z32, self.coef, self.eps, act)
+        self.ops.linear(act, self.w_down, self.b_down, residual32, "add")
+
+
 register_part("swiglu", SwiGLU)
+register_part("polynorm_ffn", PolyNormFeedForward)

@@ -61,3 +61,55 @@ class NoPositionEncoding(PositionEncoding):
 
 register_part("rotary", RotaryEncoding)
 register_part("no_position", NoPositionEncoding)
+
+
+def scaled_frequencies(dims: int, base: float, scaling=None):
+    """Frequencies of the ``dims/2`` rotated pairs, ``f_i = base^(-2i/dims)``, optionally rescaled the YaRN way, and
+    the factor on cos and sin. ``scaling`` = {factor, original, fast, slow}: a pair that turns more than ``fast``
+    times within ``original`` positions keeps its frequency, one that turns fewer than ``slow`` times has it divided
+    by ``factor``, linearly blended in between over the pair index: with
+    ``turn_dim(t) = dims * ln(original / (2 pi t)) / (2 ln base)``, ``lo = max(floor(turn_dim(fast)), 0)``,
+    ``hi = min(ceil(turn_dim(slow)), dims - 1)`` and ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` the
+    frequency is ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``, and cos and sin are multiplied by
+    ``0.1 ln(factor) + 1``. Computed in 64-bit, returned as (float64 tensor, float)."""
+    import math
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / float(dims))
+    if not scaling:
+        return f, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def turn_dim(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+    lo = max(math.floor(turn_dim(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(turn_dim(float(scaling["slow"]))), dims - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+class FrequencyRotary(PositionEncoding):
+    """Rotary positions given as a vector of frequencies instead of tables: the kernels form
+    ``angle = position * frequency`` in 32-bit themselves, for any position, and rotate INTERLEAVED pairs
+    (element 2i with 2i + 1). params: ``dims`` (rotated width), ``base``, ``scaling`` (None or the dict of
+    ``scaled_frequencies``). No tensors. ``rotary()`` is None: mixers that want tables cannot bind to it."""
+
+    graph_safe = True   # launches do not depend on which requests are in the batch
+
+    @staticmethod
+    def spec(dims: int, base: float, scaling=None) -> PartSpec:
+        return PartSpec("frequency_rotary", {"dims": dims, "base": base, "scaling": dict(scaling) if scaling else None})
+
+    def __init__(self, spec: PartSpec, tensors: Dict[str, torch.Tensor], rt: Runtime):
+        super().__init__(spec, tensors, rt)
+        self.dims = int(spec.params["dims"])
+        if self.dims <= 0 or self.dims % 2:
+            raise ValueError(f"rotated width must be positive and even, got {self.dims}")
+        f, self.magnitude = scaled_frequencies(self.dims, float(spec.params["base"]), spec.params.get("scaling"))
+        self.freq = f.to(torch.float32).to(rt.device).contiguous()
+
+    def frequencies(self):
+        """(frequencies [dims/2] float32 on the device, factor on cos and sin, dims)."""
+        return self.freq, self.magnitude, self.dims
+
+
+register_part("frequency_rotary", FrequencyRotary)

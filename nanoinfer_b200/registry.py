@@ -47,10 +47,13 @@ def get_architecture(name: str) -> Architecture:
 
 
 def config_from_json_dict(d: Mapping) -> ModelConfig:
-    """Choose the architecture by ``architectures[0]`` and read its typed configuration."""
+    """Choose the architecture by ``architectures[0]`` (or the single name ``architecture``) and read its typed
+    configuration."""
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]
     if not archs or not isinstance(archs, list) or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name)")
     return get_architecture(archs[0]).config_cls.from_json_dict(d)
 
 
@@ -95,3 +98,4 @@ def _ensure_builtin() -> None:
     _builtin_loaded = True
     from . import parts as _parts  # noqa: F401  registers the built-in parts
     from .models import qwen2 as _qwen2  # noqa: F401  registers Qwen2ForCausalLM
+    from .models import nezalorn as _nezalorn  # noqa: F401  registers Nezalorn

@@ -54,6 +54,11 @@ def _as_kept(t: torch.Tensor) -> torch.Tensor:
     raise SafetensorsError(f"unsupported tensor dtype {t.dtype}")
 
 
+def tensor_shapes(model_dir: str) -> Dict[str, tuple]:
+    """Name -> shape of every tensor in the folder's safetensors files (headers only; no data is read)."""
+    return {name: tuple(f.shape(name)) for f in open_model_files(model_dir) for name in f.names()}
+
+
 def load_tensors(model_dir: str, plan: ModelPlan) -> Dict[str, torch.Tensor]:
     """CPU tensors for every name in ``plan.tensor_specs()``; raises ``WeightError`` otherwise."""
     files = open_model_files(model_dir)

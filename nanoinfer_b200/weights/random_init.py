@@ -1,7 +1,8 @@
 """Random-weights mode: write a model folder (config.json, model.safetensors) from a
 configuration and a seed.
 
-Distributions: N(0, 0.02) for matrices, embeddings and biases, 1 + N(0, 0.1) for norm gains.
+Distributions: N(0, 0.02) for matrices, embeddings and biases, 1 + N(0, 0.1) for norm gains, N(0, 1) for "unit"
+tensors (logits of decays, coefficients of an activation), (1 + N(0, 0.3)) / n for the n weights of an average ("mix").
 Each tensor has a generator of its own, seeded from (seed, tensor name), so a tensor's values do
 not depend on which other tensors exist or in which order they are made. The reference has no
 such mode in its C++ engine; its oracle tests build ``Model(cfg)`` with framework-default
@@ -19,7 +20,7 @@ from ..config.model_config import ModelConfig, write_config_json
 from ..parts.spec import ModelPlan, TensorSpec
 from .safetensors_io import save_safetensors
 
-_STD = {"matrix": 0.02, "embedding": 0.02, "bias": 0.02}
+_STD = {"matrix": 0.02, "embedding": 0.02, "bias": 0.02, "unit": 1.0}
 
 
 def _tensor_seed(seed: int, name: str) -> int:
@@ -32,6 +33,8 @@ def random_tensor(ts: TensorSpec, seed: int, dtype: torch.dtype) -> torch.Tensor
     x = torch.randn(ts.shape, generator=g, dtype=torch.float32)
     if ts.init == "gain":
         x = 1.0 + 0.1 * x
+    elif ts.init == "mix":      # weights of an average: each near 1/n
+        x = (1.0 + 0.3 * x) / max(1, x.numel())
     elif ts.init in _STD:
         x = _STD[ts.init] * x
     else:

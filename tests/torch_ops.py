@@ -94,6 +94,136 @@ class TorchOps:
                 res[t, h] = (e / e.sum()) @ v[:, h // n_rep, :]
         out.copy_(res.view(m, -1).to(out.dtype))
 
+    # ---- row-wise and element-wise kernels of pointwise.cu ------------------------------------------
+    def poly_norm(self, z32, coef32, eps, out):
+        z = z32.double()
+        n = lambda y: y / torch.sqrt(y.pow(2).mean(-1, keepdim=True) + eps)
+        c = coef32.double()
+        out.copy_((c[0] * n(z) + c[1] * n(z ** 2) + c[2] * n(z ** 3) + c[3]).to(out.dtype))
+
+    def depth_mix(self, hist32, x32, coef32, n):
+        hist32[n - 1].copy_(x32)
+        acc = torch.zeros_like(x32, dtype=torch.float64)
+        for j in range(n):
+            acc += coef32[j].double() * hist32[j].double()
+        x32.copy_(acc.to(torch.float32))
+
+    def unary(self, in32, out, kind):
+        x = in32.double()
+        out.copy_({"tanh": torch.tanh, "copy": lambda v: v, "sigmoid": torch.sigmoid}[kind](x).to(out.dtype))
+
+    def head_norm_gate(self, o32, gate32, gain32, eps, heads, d, out):
+        m = o32.shape[0]
+        o = o32.double().view(m, heads, d)
+        o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps)
+        out.copy_((o.reshape(m, heads * d) * gain32.double() * torch.sigmoid(gate32.double())).to(out.dtype))
+
+    # ---- recurrent mixers of recurrent.cu -----------------------------------------------------------
+    def delta_rule_scan(self, r32, k32, v32, a_logit32, w_logit32, state, ctx, o32, heads, d):
+        import math
+        start = 0
+        for q_len, slot in zip(ctx.host.q_lens, ctx.host.slots):
+            S = state[slot].double().transpose(1, 2).clone()            # kept as [head, value, key]; here [head, key, value]
+            for t in range(start, start + q_len):
+                r, k, v = (x[t].double().view(heads, d) for x in (r32, k32, v32))
+                a = torch.sigmoid(a_logit32[t].double()).view(heads, d)
+                w = torch.exp(-math.exp(-0.5) * torch.sigmoid(w_logit32[t].double())).view(heads, d)
+                u = k / torch.sqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+                proj = torch.einsum("hk,hkv->hv", u, S)
+                S = w[:, :, None] * S - (a * u)[:, :, None] * proj[:, None, :] + k[:, :, None] * v[:, None, :]
+                o32[t] = torch.einsum("hkv,hk->hv", S, r).reshape(-1).to(torch.float32)
+            state[slot] = S.transpose(1, 2).to(torch.float32)
+            start += q_len
+
+    def causal_conv(self, x32, w32, bias32, state, hist_row0, ctx, u32, u_blocks, taps, blocks):
+        start = 0
+        m, width = x32.shape
+        for q_len, slot in zip(ctx.host.q_lens, ctx.host.slots):
+            hist = state[slot, hist_row0:hist_row0 + taps - 1].double()
+            padded = torch.cat([hist, x32[start:start + q_len].double()], 0)
+            u = bias32.double().expand(q_len, width).clone()
+            for j in range(taps):
+                u += padded[j:j + q_len] * w32[:, j].double()
+            u32[start:start + q_len] = u.to(torch.float32)
+            start += q_len
+        bw = width // blocks
+        u_blocks.copy_(u32.view(m, blocks, bw).transpose(0, 1).to(u_blocks.dtype))
+
+    def rglru_scan(self, u32, gates32, y_logit32, x32, softplus_lam32, state, ctx, out, taps, blocks):
+        import math
+        m, width = u32.shape
+        bw = width // blocks
+        g = gates32.double().transpose(0, 1)                                # [m, blocks, 2 bw]
+        rg = torch.sigmoid(g[..., :bw]).reshape(m, width)
+        ig = torch.sigmoid(g[..., bw:]).reshape(m, width)
+        log_a = -8.0 * rg * softplus_lam32.double()
+        a = torch.exp(log_a)
+        mult = torch.sqrt(-torch.expm1(2.0 * log_a))
+        z = y_logit32.double()
+        y = 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+        start = 0
+        for q_len, slot in zip(ctx.host.q_lens, ctx.host.slots):
+            S = state[slot, 0].double()
+            for t in range(start, start + q_len):
+                S = a[t] * S + mult[t] * ig[t] * u32[t].double()
+                out[t] = (S * y[t]).to(out.dtype)
+            state[slot, 0] = S.to(torch.float32)
+            if taps > 1:
+                joined = torch.cat([state[slot, 1:taps], x32[start:start + q_len]], 0)
+                state[slot, 1:taps] = joined[-(taps - 1):].clone()
+            start += q_len
+
+    # ---- attention through a latent (latent_attention.cu) ---------------------------------------------
+    @staticmethod
+    def _turn(x, positions, freq32, mag):
+        """Interleaved pairs of the last axis turned by position * freq (angles in 32-bit, as the kernels form them)."""
+        ang = (positions.to(torch.float32)[:, None] * freq32[None, :]).double()
+        c, s = ang.cos() * mag, ang.sin() * mag
+        while c.dim() < x.dim():
+            c, s = c.unsqueeze(1), s.unsqueeze(1)
+        out = torch.empty_like(x)
+        out[..., 0::2] = x[..., 0::2] * c - x[..., 1::2] * s
+        out[..., 1::2] = x[..., 1::2] * c + x[..., 0::2] * s
+        return out
+
+    def latent_store(self, z32, gain32, eps, freq32, mag, ctx, block_table, page_size, pages, rank, rot):
+        z = z32.double()
+        c = z[:, :rank] / torch.sqrt(z[:, :rank].pow(2).mean(-1, keepdim=True) + eps) * gain32.double()
+        kr = self._turn(z[:, rank:], ctx.positions, freq32, mag)
+        pos = ctx.positions.long()
+        page = block_table[ctx.req_index.long(), pos // page_size].long()
+        ok = page >= 0
+        pages[page[ok], 0, (pos % page_size)[ok], :] = torch.cat([c, kr], -1)[ok].to(pages.dtype)
+
+    def latent_query(self, q32, w_uk, freq32, mag, positions, qa32, heads, dn, rank, rot):
+        m = q32.shape[0]
+        q = q32.double().view(m, heads, dn + rot)
+        lat = torch.einsum("thd,hdc->thc", q[..., :dn], w_uk.double().view(heads, dn, rank))
+        qa32.copy_(torch.cat([lat, self._turn(q[..., dn:], positions, freq32, mag)], -1).reshape(m, -1).to(torch.float32))
+
+    def latent_attention(self, qa32, lat32, ctx, block_table, page_size, pages, heads, rank, rot, scale, window):
+        m = qa32.shape[0]
+        q = qa32.double().view(m, heads, rank + rot)
+        positions, req_index = ctx.positions.tolist(), ctx.req_index.tolist()
+        for t in range(m):
+            p, r = positions[t], req_index[t]
+            lo = max(0, p - window + 1) if window else 0
+            idx = torch.arange(lo, p + 1)
+            pg = block_table[r, idx // page_size].long()
+            if (pg < 0).any():
+                assert (pg < 0).all() and p == 0, "read of a position without a page"     # a padding row sees nothing
+                lat32[t] = 0
+                continue
+            rows = pages[pg, 0, idx % page_size, :].double()             # [n, rank + rot]
+            s = torch.einsum("hc,nc->hn", q[t], rows) * scale
+            w = torch.softmax(s, dim=-1)
+            lat32[t] = (w @ rows[:, :rank]).reshape(-1).to(torch.float32)
+
+    def latent_value(self, lat32, w_uv, out, heads, dv, rank):
+        m = lat32.shape[0]
+        v = torch.einsum("thc,hjc->thj", lat32.double().view(m, heads, rank), w_uv.double().view(heads, dv, rank))
+        out.copy_(v.reshape(m, heads * dv).to(out.dtype))
+
     def argmax(self, logits, out):
         out.copy_(torch.argmax(logits, dim=-1).to(out.dtype))
 
