@@ -461,6 +461,154 @@ def run_ours(args) -> dict:
     }
 
 
+# ---- another design beside the closest existing one (--design) ------------------------------------------
+# Layer sizes that resemble a real model's, small enough for minutes: a Nezalorn stack (delta rule, two gated
+# recurrences, latent attention; the last attention layer reads the first one's cached latents) and the Qwen2
+# decoder of the same width, depth and vocabulary, with about the same matrix parameters per layer (PolyNorm has
+# two feed-forward matrices where SwiGLU has three).
+DESIGN_SIZES = {
+    "1k": {"width": 1024, "heads": 16, "head_dim": 64, "ff_swiglu": 2816, "rot": 32, "kv_rank": 128, "q_rank": 384,
+           "blocks": 8, "window": 1024, "vocab": 32000, "layers": 8},
+    "2k": {"width": 2048, "heads": 16, "head_dim": 128, "ff_swiglu": 5632, "rot": 64, "kv_rank": 128, "q_rank": 768,
+           "blocks": 16, "window": 1024, "vocab": 32000, "layers": 8},
+}
+
+
+def design_configs(size: dict):
+    w, h, d = size["width"], size["heads"], size["head_dim"]
+    ff = {"kind": "dense", "ff": size["ff_swiglu"] * 3 // 2}
+    lat = {"heads": h, "dim": d, "rot_dim": size["rot"], "vdim": d, "q_rank": size["q_rank"], "kv_rank": size["kv_rank"],
+           "mask": {"size": size["window"]}, "scale": (d + size["rot"]) ** -0.5,
+           "rot": {"dims": size["rot"], "base": 10000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    delta = {"type": "general_delta", "mixer": {"heads": h, "dim": d, "decay_rank": 64}, "mlp": ff}
+    lru = {"type": "rglru", "mixer": {"width": w, "conv": 4, "blocks": size["blocks"]}, "mlp": ff}
+    layers = []
+    for i in range(size["layers"]):
+        kind = i % 4
+        if kind == 0:
+            layers.append(delta)
+        elif kind in (1, 2):
+            layers.append(lru)
+        else:
+            m = dict(lat) if i == 3 else dict(lat, kv_from=3)
+            layers.append({"type": "latent_attention", "mixer": m, "mlp": ff})
+    nez = {"architecture": "Nezalorn", "vocab": size["vocab"], "width": w, "norm": {"eps": 1e-5}, "layers": layers}
+    qwen = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": size["layers"], "hidden_size": w,
+            "num_attention_heads": h, "num_key_value_heads": 2, "head_dim": d, "intermediate_size": size["ff_swiglu"],
+            "vocab_size": size["vocab"], "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+            "max_position_embeddings": 32768, "use_sliding_window": False, "hidden_act": "silu", "torch_dtype": "bfloat16"}
+    return nez, qwen
+
+
+def run_design(args) -> dict:
+    """Prefill and decode throughput of the Nezalorn design beside the Qwen2 decoder at equal size (random weights,
+    bfloat16, device-timed with CUDA events), and where one eager step's time goes, launch kind by launch kind."""
+    import numpy as np
+    import torch
+    from nanoinfer_b200 import load_model
+    from nanoinfer_b200.engine import StepEntry
+    from nanoinfer_b200.registry import config_from_json_dict
+    from nanoinfer_b200.weights import write_random_model
+    pk = peaks()
+    t_pre, batch, ctx = args.prefill_tokens, args.batch, min(args.context, 2048)
+    steps, warmup = min(args.steps, 64), max(3, args.warmup)
+    out = {"impl": "ours", "design": "nezalorn", "dtype": "bf16", "data": "synthetic: seeded random weights and random token ids",
+           "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]},
+           "config": {"prefill_tokens": t_pre, "decode_batch": batch, "decode_context": ctx, "page_size": 16}, "sizes": {}}
+    for name in (args.design_sizes.split(",") if args.design_sizes else sorted(DESIGN_SIZES)):
+        size = DESIGN_SIZES[name]
+        row = {}
+        for label, cfg_json in zip(("nezalorn", "qwen2"), design_configs(size)):
+            rng = np.random.default_rng(0)
+            tmp = tempfile.mkdtemp(prefix="nanoinfer_b200_design_")
+            try:
+                write_random_model(config_from_json_dict(cfg_json), tmp, seed=0)
+                model = load_model(tmp, dtype="bfloat16", page_size=16, num_pages=(batch + 1) * (ctx // 16 + 8) + t_pre // 16 + 8,
+                                   max_batch=batch + 1, max_tokens_per_step=4096, cuda_graphs=not args.no_graphs)
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            engine, ops, vocab = model.engine, model.engine.rt.ops, size["vocab"]
+
+            def timed(fn, n):
+                torch.cuda.synchronize()
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                for _ in range(n):
+                    fn()
+                e.record()
+                torch.cuda.synchronize()
+                return s.elapsed_time(e) / n
+
+            # prefill: one prompt of t_pre tokens, logits of the last (3 warm-up prompts, the median of 7)
+            pre = []
+            for i in range(10):
+                rc = engine.open(f"p{i}")
+                ids = rng.integers(0, vocab, t_pre).astype(np.int32)
+                ms = timed(lambda: engine.step([StepEntry(rc, ids, [t_pre - 1])]), 1)
+                engine.close(rc)
+                if i >= 3:
+                    pre.append(ms)
+            # decode: `batch` requests holding ctx tokens each go on token by token (contexts grow by `steps`)
+            reqs = [engine.open(f"d{i}") for i in range(batch)]
+            for rc in reqs:
+                done = 0
+                while done < ctx - warmup - steps:
+                    n = min(2048, ctx - warmup - steps - done)
+                    engine.step([StepEntry(rc, rng.integers(0, vocab, n).astype(np.int32), [])])
+                    done += n
+            pick = torch.empty(batch, dtype=torch.int32, device=engine.device)
+
+            def one():
+                logits = engine.step([StepEntry(rc, [int(rng.integers(0, vocab))], [0]) for rc in reqs], borrow_logits=True)
+                ops.argmax(logits, pick)
+            for _ in range(warmup):
+                one()
+            l0 = ops.launches + engine.graph_launches
+            with ClockSampler() as cs:
+                dec_ms = timed(one, steps)
+            launches = ops.launches + engine.graph_launches - l0
+            # where the time goes: one eager prompt and one eager decode step with an event behind every launch
+            kinds = {}
+            if args.breakdown:
+                eager = ops
+                for phase in ("prefill", "decode"):
+                    if phase == "prefill":
+                        rc = engine.open("t")
+                        ids = rng.integers(0, vocab, t_pre).astype(np.int32)
+                        entries = [StepEntry(rc, ids, [t_pre - 1])]
+                    else:
+                        entries = [StepEntry(rc, [int(rng.integers(0, vocab))], [0]) for rc in reqs]
+                    graphs = (engine._graphs, engine._portion_graphs)
+                    engine._graphs = engine._portion_graphs = None
+                    try:
+                        eager.time_ops(True)
+                        engine.step(entries)
+                        agg = {}
+                        for what, us in eager.op_times():
+                            n, tot = agg.get(what, (0, 0.0))
+                            agg[what] = (n + 1, tot + us)
+                        eager.time_ops(False)
+                    finally:
+                        engine._graphs, engine._portion_graphs = graphs
+                    kinds[phase] = {k: {"n": n, "us": round(t, 1)} for k, (n, t) in sorted(agg.items(), key=lambda kv: -kv[1][1])}
+                    if phase == "prefill":
+                        engine.close(rc)
+            for rc in reqs:
+                engine.close(rc)
+            pre_ms = statistics.median(pre)
+            row[label] = {"prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(t_pre / pre_ms * 1e3, 1),
+                          "decode_ms_per_step": round(dec_ms, 4), "decode_tok_s": round(batch / dec_ms * 1e3, 1),
+                          "weight_bytes": model.weight_bytes()[0], "decode_launches": launches, "clocks": cs.summary()}
+            if kinds:
+                row[label]["launch_kinds_us"] = kinds
+            del model, engine, ops
+            torch.cuda.empty_cache()
+        row["ratio_prefill"] = round(row["nezalorn"]["prefill_tok_s"] / row["qwen2"]["prefill_tok_s"], 3)
+        row["ratio_decode"] = round(row["nezalorn"]["decode_tok_s"] / row["qwen2"]["decode_tok_s"], 3)
+        out["sizes"][name] = dict(row, size=size)
+    return out
+
+
 def serve_workload(model, args, rng, vocab: int, layers: int) -> dict:
     """A mixed continuous batch through the scheduler: 64 requests with prompts of 128 to 2,048 random ids
     and 256 decoded tokens each, all queued at once; prompts are cut under a budget of 2,048 tokens a step
@@ -595,6 +743,10 @@ def main() -> int:
                     help="add a 'kernels' block: where the time of a decode step and of a prompt portion goes, kernel kind by "
                          "kind, with bytes or FLOPs and the fraction of the measured peak")
     ap.add_argument("--shape", default="0.5b", choices=sorted(SHAPES), help="layer sizes: the family's 0.5B (default), 1.5B or 7B")
+    ap.add_argument("--design", default=None, choices=["nezalorn"],
+                    help="instead of the headline workload: prefill and decode throughput of this design beside the Qwen2 "
+                         "decoder at equal size (--design-sizes, --prefill-tokens, --batch, --context up to 2048, --breakdown)")
+    ap.add_argument("--design-sizes", default="", help="comma-separated names of DESIGN_SIZES (default: all)")
     args = ap.parse_args()
     MODEL.update(SHAPES[args.shape])
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
@@ -605,6 +757,9 @@ def main() -> int:
     if args.steps + args.warmup + 2 >= args.context:
         print(json.dumps({"unavailable": "steps + warmup must be smaller than the context"}))
         return 2
+    if args.design and args.impl == "ours":
+        print(json.dumps(run_design(args)), flush=True)
+        return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result), flush=True)
     return 0

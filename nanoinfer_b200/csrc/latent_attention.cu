@@ -67,19 +67,20 @@ NIB_API int nib_latent_store(const float* z, int ldz, const float* gain, float e
 }
 
 // ---------------------------------------------------------------------------------- queries into the latent space
-// q: [tokens, heads, dn + rot] floats. qa: [tokens, heads, rank + rot] floats:
-//   qa[:rank] = sum_d q[d] * w_uk[h*dn + d, :]   (w_uk: [heads*dn, rank], as stored),   qa[rank:] = rotated q[dn:].
+// q: [tokens, heads, dn + rot] floats. qa: [tokens, heads, ldq] of TQ (float for the general kernel, bfloat16 rows
+// padded with zeros for the tensor-core kernels):
+//   qa[:rank] = sum_d q[d] * w_uk[h*dn + d, :]   (w_uk: [heads*dn, rank], as stored),   qa[rank:rank+rot] = rotated q[dn:].
 // One warp per (token, head); lanes over the latent's columns, so the rows of w_uk are read coalesced.
-template <typename T>
+template <typename T, typename TQ>
 __global__ void __launch_bounds__(LAT_WARPS * 32)
-latent_query_kernel(const float* __restrict__ q, int ldq, const T* __restrict__ w_uk, const float* __restrict__ freq, float mag,
-                    const int* __restrict__ positions, float* __restrict__ qa, int tokens, int heads, int dn, int rank, int rot) {
+latent_query_kernel(const float* __restrict__ q, int ldq_in, const T* __restrict__ w_uk, const float* __restrict__ freq, float mag,
+                    const int* __restrict__ positions, TQ* __restrict__ qa, int ldq, int tokens, int heads, int dn, int rank, int rot) {
     const long long w = (long long)blockIdx.x * LAT_WARPS + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (w >= (long long)tokens * heads) return;
     const int t = (int)(w / heads), h = (int)(w % heads);
-    const float* qr = q + (size_t)t * ldq + (size_t)h * (dn + rot);
-    float* o = qa + ((size_t)t * heads + h) * (rank + rot);
+    const float* qr = q + (size_t)t * ldq_in + (size_t)h * (dn + rot);
+    TQ* o = qa + (size_t)w * ldq;
     const T* wh = w_uk + (size_t)h * dn * rank;
     for (int c0 = 0; c0 < rank; c0 += 32 * 4) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -94,7 +95,7 @@ latent_query_kernel(const float* __restrict__ q, int ldq, const T* __restrict__ 
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int c = c0 + lane + 32 * i;
-            if (c < rank) o[c] = acc[i];
+            if (c < rank) Elem<TQ>::store(o + c, acc[i]);
         }
     }
     const int pos = positions[t];
@@ -102,22 +103,27 @@ latent_query_kernel(const float* __restrict__ q, int ldq, const T* __restrict__ 
         const float ang = (float)pos * freq[i];
         const float cs = cosf(ang) * mag, sn = sinf(ang) * mag;
         const float a = qr[dn + 2 * i], b = qr[dn + 2 * i + 1];
-        o[rank + 2 * i] = a * cs - b * sn;
-        o[rank + 2 * i + 1] = b * cs + a * sn;
+        Elem<TQ>::store(o + rank + 2 * i, a * cs - b * sn);
+        Elem<TQ>::store(o + rank + 2 * i + 1, b * cs + a * sn);
     }
+    for (int c = rank + rot + lane; c < ldq; c += 32) Elem<TQ>::store(o + c, 0.f);
 }
 
-NIB_API int nib_latent_query(const float* q, int ldq, const void* w_uk, const float* freq, float mag, const int* positions,
-                             float* qa, int tokens, int heads, int dn, int rank, int rot, int dtype, cudaStream_t stream) {
-    NIB_REQUIRE(tokens >= 0 && heads > 0 && dn > 0 && rank > 0 && rot >= 0 && rot % 2 == 0, "latent_query: bad sizes");
+// dtype: the weights' type; q_dtype: the type of qa's elements; ldq: qa's row width per (token, head), >= rank + rot.
+NIB_API int nib_latent_query(const float* q, int ldq_in, const void* w_uk, const float* freq, float mag, const int* positions,
+                             void* qa, int ldq, int q_dtype, int tokens, int heads, int dn, int rank, int rot, int dtype,
+                             cudaStream_t stream) {
+    NIB_REQUIRE(tokens >= 0 && heads > 0 && dn > 0 && rank > 0 && rot >= 0 && rot % 2 == 0 && ldq >= rank + rot, "latent_query: bad sizes");
     if (tokens == 0) return 0;
     const int grid = ceil_div((long long)tokens * heads, LAT_WARPS);
-    if (dtype == NIB_F32)
-        latent_query_kernel<float><<<grid, LAT_WARPS * 32, 0, stream>>>(q, ldq, (const float*)w_uk, freq, mag, positions, qa, tokens, heads, dn, rank, rot);
-    else if (dtype == NIB_BF16)
-        latent_query_kernel<__nv_bfloat16><<<grid, LAT_WARPS * 32, 0, stream>>>(q, ldq, (const __nv_bfloat16*)w_uk, freq, mag, positions, qa, tokens, heads, dn, rank, rot);
+    if (dtype == NIB_F32 && q_dtype == NIB_F32)
+        latent_query_kernel<float, float><<<grid, LAT_WARPS * 32, 0, stream>>>(q, ldq_in, (const float*)w_uk, freq, mag, positions, (float*)qa, ldq, tokens, heads, dn, rank, rot);
+    else if (dtype == NIB_BF16 && q_dtype == NIB_F32)
+        latent_query_kernel<__nv_bfloat16, float><<<grid, LAT_WARPS * 32, 0, stream>>>(q, ldq_in, (const __nv_bfloat16*)w_uk, freq, mag, positions, (float*)qa, ldq, tokens, heads, dn, rank, rot);
+    else if (dtype == NIB_BF16 && q_dtype == NIB_BF16)
+        latent_query_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, LAT_WARPS * 32, 0, stream>>>(q, ldq_in, (const __nv_bfloat16*)w_uk, freq, mag, positions, (__nv_bfloat16*)qa, ldq, tokens, heads, dn, rank, rot);
     else
-        NIB_REQUIRE(false, "latent_query: unknown dtype %d", dtype);
+        NIB_REQUIRE(false, "latent_query: unsupported types %d / %d", dtype, q_dtype);
     NIB_LAUNCH_CHECK();
     return 0;
 }

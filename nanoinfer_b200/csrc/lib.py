@@ -82,7 +82,8 @@ class Kernels:
                      "nib_sm_count", "nib_gemm_smallm_qkv", "nib_gemm_smallm_qkv_supported", "nib_gemm_tc_qkv",
                      "nib_gemm_tc_qkv_supported", "nib_poly_norm", "nib_depth_mix", "nib_unary", "nib_head_norm_gate",
                      "nib_delta_rule_scan", "nib_causal_conv", "nib_rglru_scan", "nib_latent_store", "nib_latent_query",
-                     "nib_latent_attention", "nib_latent_value"):
+                     "nib_latent_attention", "nib_latent_value", "nib_latent_attention_mma", "nib_latent_attention_mma_supported",
+                     "nib_latent_attention_mma_qwidth"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -661,30 +662,81 @@ class Kernels:
             _ptr(ctx.req_index), _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), _ptr(pages),
             c_int(pages.shape[0]), c_int(z32.shape[0]), c_int(rank), c_int(rot), c_int(_DT[pages.dtype]), self._stream()), "latent_store")
 
-    def latent_query(self, q32, w_uk, freq32, mag, positions, qa32, heads, dn, rank, rot):
-        """qa32[t, h] = [W_uk,h^T q32[t, h, :dn] | q32[t, h, dn:] rotated]; w_uk: [heads * dn, rank] as stored."""
-        self._rows(q32, torch.float32, "latent_query q"); _need(w_uk, None, "latent_query w_uk"); _need(qa32, torch.float32, "latent_query qa")
+    def _latent_mma(self, dtype, rank, rot) -> bool:
+        """Whether the tensor-core kernels run the attention over rows of ``rank + rot`` elements of ``dtype``."""
+        return dtype == torch.bfloat16 and not self.options.force_general_attention \
+            and self._lib.nib_latent_attention_mma_supported(c_int(rank), c_int(rot)) == 1
+
+    def latent_query_layout(self, dtype, rank, rot):
+        """(elements per (token, head), element type) of the query rows that ``latent_attention`` reads for a cache of
+        ``dtype``: floats of rank + rot for the general kernel, bfloat16 rows padded to a multiple of 16 for the
+        tensor-core kernels."""
+        if self._latent_mma(dtype, rank, rot):
+            return self._lib.nib_latent_attention_mma_qwidth(c_int(rank), c_int(rot)), torch.bfloat16
+        return rank + rot, torch.float32
+
+    def latent_query(self, q32, w_uk, freq32, mag, positions, qa, heads, dn, rank, rot):
+        """qa[t, h] = [W_uk,h^T q32[t, h, :dn] | q32[t, h, dn:] rotated | zeros]; w_uk: [heads * dn, rank] as stored;
+        qa: [tokens, heads * width] in the layout ``latent_query_layout`` gives."""
+        self._rows(q32, torch.float32, "latent_query q"); _need(w_uk, None, "latent_query w_uk"); _need(qa, None, "latent_query qa")
         _need(freq32, torch.float32, "latent_query freq")
         m = q32.shape[0]
-        if q32.shape[1] != heads * (dn + rot) or tuple(w_uk.shape) != (heads * dn, rank) or tuple(qa32.shape) != (m, heads * (rank + rot)):
+        ldq = qa.shape[1] // heads
+        if q32.shape[1] != heads * (dn + rot) or tuple(w_uk.shape) != (heads * dn, rank) or qa.shape[0] != m \
+                or qa.shape[1] != heads * ldq or ldq < rank + rot:
             raise KernelError("latent_query: shapes do not fit")
         self._check(self._lib.nib_latent_query(_ptr(q32), c_int(q32.stride(0)), _ptr(w_uk), _ptr(freq32), c_float(mag), _ptr(positions),
-                                               _ptr(qa32), c_int(m), c_int(heads), c_int(dn), c_int(rank), c_int(rot),
-                                               c_int(_DT[w_uk.dtype]), self._stream()), "latent_query")
+                                               _ptr(qa), c_int(ldq), c_int(_DT[qa.dtype]), c_int(m), c_int(heads), c_int(dn), c_int(rank),
+                                               c_int(rot), c_int(_DT[w_uk.dtype]), self._stream()), "latent_query")
 
-    def latent_attention(self, qa32, lat32, ctx, block_table, page_size, pages, heads, rank, rot, scale, window):
-        """lat32[t, h] = sum_j softmax_j((qa32[t, h] . row_j) * scale) * row_j[:rank] over the cached rows of the token's
-        request at positions lo..own (lo = own - window + 1 with a window)."""
-        _need(qa32, torch.float32, "latent_attention qa"); _need(lat32, torch.float32, "latent_attention out"); _need(pages, None, "latent_attention pages")
+    def latent_attention(self, qa, lat32, ctx, block_table, page_size, pages, heads, rank, rot, scale, window):
+        """lat32[t, h] = sum_j softmax_j((qa[t, h] . row_j) * scale) * row_j[:rank] over the cached rows of the token's
+        request at positions lo..own (lo = own - window + 1 with a window). bfloat16 rows of a supported width run on
+        the tensor cores: the leading requests that bring one token each go to the decode kernel (keys split over
+        CTAs), the others to the kernel for prompt portions; everything else runs the general kernel."""
+        _need(qa, None, "latent_attention qa"); _need(lat32, torch.float32, "latent_attention out"); _need(pages, None, "latent_attention pages")
         _need(block_table, torch.int32, "block_table", contiguous=False)
-        m = qa32.shape[0]
-        if tuple(qa32.shape) != (m, heads * (rank + rot)) or tuple(lat32.shape) != (m, heads * rank) \
+        m = qa.shape[0]
+        qw, qdt = self.latent_query_layout(pages.dtype, rank, rot)
+        if tuple(qa.shape) != (m, heads * qw) or qa.dtype != qdt or tuple(lat32.shape) != (m, heads * rank) \
                 or tuple(pages.shape[1:]) != (1, page_size, rank + rot) or block_table.stride(1) != 1:
             raise KernelError("latent_attention: shapes do not fit")
-        self._check(self._lib.nib_latent_attention(
-            _ptr(qa32), _ptr(lat32), _ptr(ctx.positions), _ptr(ctx.req_index), _ptr(block_table), c_int(block_table.stride(0)),
-            c_int(page_size), _ptr(pages), c_int(pages.shape[0]), c_int(m), c_int(heads), c_int(rank), c_int(rot), c_float(scale),
-            c_int(window), c_int(_DT[pages.dtype]), self._stream()), "latent_attention")
+        bt_stride = block_table.stride(0)
+        if qdt == torch.float32:
+            self._check(self._lib.nib_latent_attention(
+                _ptr(qa), _ptr(lat32), _ptr(ctx.positions), _ptr(ctx.req_index), _ptr(block_table), c_int(bt_stride),
+                c_int(page_size), _ptr(pages), c_int(pages.shape[0]), c_int(m), c_int(heads), c_int(rank), c_int(rot), c_float(scale),
+                c_int(window), c_int(_DT[pages.dtype]), self._stream()), "latent_attention")
+            return
+        q_lens, ctx_lens = ctx.host.q_lens, ctx.host.ctx_lens
+        n_req = len(q_lens)
+        n_dec = 0
+        while n_dec < n_req and q_lens[n_dec] == 1:
+            n_dec += 1
+        tail = (c_int(heads), c_int(rank), c_int(rot), c_float(scale), c_int(window))
+        if n_dec:
+            keys = max(ctx_lens[:n_dec])
+            keys = min(keys, window) if window > 0 else keys
+            tiles = -(-keys // 64) + 1
+            most = max(1, (4 * self.sm_count) // max(1, n_dec * -(-heads // 16)))
+            splits = self.options.fixed_decode_splits or max(1, min(-(-tiles // 2), most, 32))
+            part_o = part_ml = None
+            if splits > 1:
+                part_o = torch.empty(n_dec * heads * splits * 192, dtype=torch.float32, device=qa.device)
+                part_ml = torch.empty(n_dec * heads * splits * 2, dtype=torch.float32, device=qa.device)
+            self._check(self._lib.nib_latent_attention_mma(
+                c_int(1), _ptr(qa), _ptr(lat32), _ptr(ctx.q_start), _ptr(ctx.ctx_lens), _ptr(block_table), c_int(bt_stride),
+                c_int(page_size), _ptr(pages), c_int(pages.shape[0]), c_int(n_dec), c_int(1), *tail, c_int(splits),
+                _ptr(part_o), _ptr(part_ml), self._stream()), "latent attention decode (mma)")
+            if splits > 1:
+                self.launches += 1
+        if n_dec < n_req:
+            # rows of qa and lat32 are addressed through q_start, whose entries count from the step's first row
+            self._check(self._lib.nib_latent_attention_mma(
+                c_int(0), _ptr(qa), _ptr(lat32), c_void_p(ctx.q_start.data_ptr() + 4 * n_dec), c_void_p(ctx.ctx_lens.data_ptr() + 4 * n_dec),
+                c_void_p(block_table.data_ptr() + 4 * n_dec * bt_stride), c_int(bt_stride), c_int(page_size), _ptr(pages),
+                c_int(pages.shape[0]), c_int(n_req - n_dec), c_int(max(q_lens[n_dec:])), *tail, c_int(1), _ptr(None), _ptr(None),
+                self._stream()), "latent attention prefill (mma)")
 
     def latent_value(self, lat32, w_uv, out, heads, dv, rank):
         """out[t, h*dv + j] = w_uv[h*dv + j, :] . lat32[t, h, :]."""

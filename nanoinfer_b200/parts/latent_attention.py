@@ -97,10 +97,11 @@ class LatentAttention(Mixer):
         ops.rmsnorm(cq32, self.g_dq, self.eps, cq)
         q32 = torch.empty((m, self.heads * (self.dim + self.rot_dim)), dtype=torch.float32, device=dev)
         ops.linear(cq, self.w_uq, None, q32, "f32")
-        qa32 = torch.empty((m, self.heads * (self.kv_rank + self.rot_dim)), dtype=torch.float32, device=dev)
-        ops.latent_query(q32, self.w_uk, freq, mag, ctx.positions, qa32, self.heads, self.dim, self.kv_rank, self.rot_dim)
+        q_width, q_dtype = ops.latent_query_layout(pages.dtype, self.kv_rank, self.rot_dim)     # what the attention kernel reads
+        qa = torch.empty((m, self.heads * q_width), dtype=q_dtype, device=dev)
+        ops.latent_query(q32, self.w_uk, freq, mag, ctx.positions, qa, self.heads, self.dim, self.kv_rank, self.rot_dim)
         lat32 = torch.empty((m, self.heads * self.kv_rank), dtype=torch.float32, device=dev)
-        ops.latent_attention(qa32, lat32, ctx, cache.block_table, cache.page_size, pages, self.heads, self.kv_rank,
+        ops.latent_attention(qa, lat32, ctx, cache.block_table, cache.page_size, pages, self.heads, self.kv_rank,
                              self.rot_dim, self.scale, self.window)
         attn = torch.empty((m, self.heads * self.vdim), dtype=self.rt.dtype, device=dev)
         ops.latent_value(lat32, self.w_uv, attn, self.heads, self.vdim, self.kv_rank)

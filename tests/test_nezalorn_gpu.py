@@ -225,28 +225,44 @@ def test_latent_store_and_query(ops, dtype, rank, rot, page):
     assert_close(out, oref, dtype, "values out of the latent space")
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("window,page", [(0, 4), (5, 4), (32, 16), (33, 8), (64, 16)])
-def test_latent_attention_over_pages_and_windows(ops, dtype, window, page):
-    heads, rank, rot = 3, 24, 8
-    q_lens, before = [1, 70, 1, 9, 1], [0, 0, 131, 60, 63]          # first token; a prompt; decoding far in; a portion; a page's edge
+def _query_rows(ops, values, dtype, heads, rank, rot):
+    """``values`` [m, heads, rank + rot] floats in the layout the attention kernel reads for a cache of ``dtype``;
+    returns (the rows for the kernel, the values it will see as floats)."""
+    m = values.shape[0]
+    qw, qdt = ops.latent_query_layout(dtype, rank, rot)
+    qa = torch.zeros(m, heads, qw, dtype=qdt, device=DEV)
+    qa[:, :, :rank + rot] = values.to(qdt)
+    return qa.view(m, heads * qw), qa[:, :, :rank + rot].float().reshape(m, -1)
+
+
+@pytest.mark.parametrize("dtype,general", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
+@pytest.mark.parametrize("window,page", [(0, 4), (5, 4), (32, 16), (33, 8), (64, 16), (200, 16)])
+@pytest.mark.parametrize("heads,rank,rot", [(3, 24, 8), (16, 64, 16), (20, 128, 32)])
+def test_latent_attention_over_pages_and_windows(ops, dtype, general, window, page, heads, rank, rot):
+    """First tokens, a prompt, decoding far into a sequence, a portion that starts inside a page, a token on a page's
+    edge: one-token requests lead the batch (they take the decode kernel), with contexts long enough for split keys."""
+    k = ops.with_options(force_general_attention=True) if general else ops
+    q_lens, before = [1, 1, 1, 70, 9], [0, 331, 63, 0, 60]
     ctx, bt, num_pages = batch(q_lens, before, page_size=page)
     m = sum(q_lens)
     pages = rnd(num_pages, 1, page, rank + rot, seed=1).to(dtype)
-    qa = rnd(m, heads * (rank + rot), seed=2)
+    qa, seen = _query_rows(k, rnd(m, heads, rank + rot, seed=2), dtype, heads, rank, rot)
     lat = torch.empty(m, heads * rank, device=DEV)
-    ops.latent_attention(qa, lat, ctx, bt, page, pages, heads, rank, rot, 0.3, window)
+    k.latent_attention(qa, lat, ctx, bt, page, pages, heads, rank, rot, 0.3, window)
     ref = torch.empty(m, heads * rank)
-    TorchOps().latent_attention(qa.cpu(), ref, to_cpu(ctx), bt.cpu(), page, pages.cpu(), heads, rank, rot, 0.3, window)
-    assert_close(lat, ref, torch.float32, "latent attention")
+    TorchOps().latent_attention(seen.cpu(), ref, to_cpu(ctx), bt.cpu(), page, pages.cpu(), heads, rank, rot, 0.3, window)
+    # the tensor-core kernels round the softmax weights to bfloat16 before they meet the values
+    assert_close(lat, ref, torch.float32 if (dtype == torch.float32 or general) else torch.bfloat16, "latent attention")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("decode", [False, True])
-@pytest.mark.parametrize("window,page", [(6, 4), (32, 8), (40, 16), (129, 16)])
-def test_a_key_at_the_windows_edge_is_seen_and_the_one_before_is_not(ops, window, page, decode):
+@pytest.mark.parametrize("window,page", [(6, 4), (32, 8), (40, 16), (64, 16), (129, 16)])
+def test_a_key_at_the_windows_edge_is_seen_and_the_one_before_is_not(ops, window, page, decode, dtype):
     """All cached rows are small but one, which matches the query and carries a mark in its latent. A query whose
-    window just reaches the row returns the mark; one position later it is gone. In a prompt's portion and decoded."""
-    heads, rank, rot = 2, 16, 4
+    window just reaches the row returns the mark; one position later it is gone. In a prompt's portion and decoded,
+    on the general kernel (32-bit rows) and on the tensor-core kernels (bfloat16 rows)."""
+    heads, rank, rot = 2, 16, 8
     edge = 37                                     # the marked row's position
     last = edge + window                          # sees edge+1 .. edge+window
     if decode:
@@ -254,15 +270,15 @@ def test_a_key_at_the_windows_edge_is_seen_and_the_one_before_is_not(ops, window
     else:
         q_lens, before = [window + 3], [edge - 1]
     ctx, bt, num_pages = batch(q_lens, before, page_size=page, seed=3)
-    pages = rnd(num_pages, 1, page, rank + rot, seed=1, scale=0.01)
-    req_of_edge = 0
+    pages = rnd(num_pages, 1, page, rank + rot, seed=1, scale=0.01).to(dtype)
     for r in range(len(q_lens)):
         pg = bt[r, edge // page].item()
         pages[pg, 0, edge % page, :] = 0
         pages[pg, 0, edge % page, 0] = 5.0        # matches the query below
         pages[pg, 0, edge % page, 1] = 9.0        # the mark
-    qa = torch.zeros(sum(q_lens), heads * (rank + rot), device=DEV)
-    qa.view(-1, heads, rank + rot)[:, :, 0] = 4.0
+    values = torch.zeros(sum(q_lens), heads, rank + rot, device=DEV)
+    values[:, :, 0] = 4.0
+    qa, _ = _query_rows(ops, values, dtype, heads, rank, rot)
     lat = torch.empty(sum(q_lens), heads * rank, device=DEV)
     ops.latent_attention(qa, lat, ctx, bt, page, pages, heads, rank, rot, 1.0, window)
     pos = ctx.positions.tolist()

@@ -195,6 +195,9 @@ class TorchOps:
         ok = page >= 0
         pages[page[ok], 0, (pos % page_size)[ok], :] = torch.cat([c, kr], -1)[ok].to(pages.dtype)
 
+    def latent_query_layout(self, dtype, rank, rot):
+        return rank + rot, torch.float32
+
     def latent_query(self, q32, w_uk, freq32, mag, positions, qa32, heads, dn, rank, rot):
         m = q32.shape[0]
         q = q32.double().view(m, heads, dn + rot)
