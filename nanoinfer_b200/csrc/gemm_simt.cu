@@ -136,3 +136,42 @@ NIB_API int nib_gemm_simt(const void* A, const void* W, const float* bias, void*
     if (dtype == NIB_BF16) return launch_simt<__nv_bfloat16>(A, W, bias, out, M, N, K, lda, ldo, epi, stream);
     NIB_REQUIRE(false, "gemm: unknown dtype %d", dtype);
 }
+
+// ---------------------------------------------------------------------------------- block-diagonal product, few tokens
+// out[b, t, n] = bias[b, n] + sum_k a[b, t, k] * w[b, n, k] for `blocks` independent square-ish blocks and a handful
+// of tokens: one warp per (block, output feature) keeps its weight row in registers and walks the tokens, so a
+// decode step reads every weight once and needs one launch for all blocks. a: [blocks, tokens, k] of T,
+// w: [blocks, n, k] of T, bias: [blocks, n] floats or null, out: [blocks, tokens, n] floats.
+template <typename T>
+__global__ void __launch_bounds__(128)
+block_diag_smallm_kernel(const T* __restrict__ a, const T* __restrict__ w, const float* __restrict__ bias, float* __restrict__ out,
+                         int blocks, int tokens, int n, int k) {
+    const long long wid = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)blocks * n) return;
+    const int b = (int)(wid / n), f = (int)(wid % n);
+    const T* wr = w + ((size_t)b * n + f) * k;
+    const float bv = bias ? bias[(size_t)b * n + f] : 0.f;
+    for (int t = 0; t < tokens; ++t) {
+        const T* ar = a + ((size_t)b * tokens + t) * k;
+        float acc = 0.f;
+        for (int c = lane; c < k; c += 32) acc = fmaf(Elem<T>::load(wr + c), Elem<T>::load(ar + c), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) out[((size_t)b * tokens + t) * n + f] = acc + bv;
+    }
+}
+
+NIB_API int nib_block_diag_smallm(const void* a, const void* w, const float* bias, float* out, int blocks, int tokens, int n, int k,
+                                  int dtype, cudaStream_t stream) {
+    NIB_REQUIRE(blocks > 0 && tokens >= 0 && n > 0 && k > 0, "block-diagonal product: bad sizes");
+    if (tokens == 0) return 0;
+    const int grid = ceil_div((long long)blocks * n, 4);
+    if (dtype == NIB_F32)
+        block_diag_smallm_kernel<float><<<grid, 128, 0, stream>>>((const float*)a, (const float*)w, bias, out, blocks, tokens, n, k);
+    else if (dtype == NIB_BF16)
+        block_diag_smallm_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, bias, out, blocks, tokens, n, k);
+    else
+        NIB_REQUIRE(false, "block-diagonal product: unknown dtype %d", dtype);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}

@@ -83,7 +83,7 @@ class Kernels:
                      "nib_gemm_tc_qkv_supported", "nib_poly_norm", "nib_depth_mix", "nib_unary", "nib_head_norm_gate",
                      "nib_delta_rule_scan", "nib_causal_conv", "nib_rglru_scan", "nib_latent_store", "nib_latent_query",
                      "nib_latent_attention", "nib_latent_value", "nib_latent_attention_mma", "nib_latent_attention_mma_supported",
-                     "nib_latent_attention_mma_qwidth"):
+                     "nib_latent_attention_mma_qwidth", "nib_block_diag_smallm"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -601,6 +601,24 @@ class Kernels:
                                                  _ptr(out), c_int(out.stride(0)), c_int(m), c_int(heads), c_int(d), c_float(eps),
                                                  c_int(_DT[out.dtype]), self._stream()), "head_norm_gate")
 
+    def block_diag_linear(self, a_blocks, w_blocks, bias32, out32):
+        """out32[b] = a_blocks[b] . w_blocks[b]^T + bias32[b] for every block b: a_blocks [blocks, tokens, k],
+        w_blocks [blocks, n, k], bias32 [blocks, n] or None, out32 [blocks, tokens, n] floats. Up to 16 tokens take
+        one launch for all blocks (a decode step); more tokens run a product per block on the matrix kernels."""
+        _need(a_blocks, None, "block_diag_linear a"); _need(w_blocks, a_blocks.dtype, "block_diag_linear w"); _need(out32, torch.float32, "block_diag_linear out")
+        nb, m, k = a_blocks.shape
+        n = w_blocks.shape[1]
+        if tuple(w_blocks.shape) != (nb, n, k) or tuple(out32.shape) != (nb, m, n) or (bias32 is not None and tuple(bias32.shape) != (nb, n)):
+            raise KernelError("block_diag_linear: shapes do not fit")
+        if m <= 16:
+            if bias32 is not None:
+                _need(bias32, torch.float32, "block_diag_linear bias")
+            self._check(self._lib.nib_block_diag_smallm(_ptr(a_blocks), _ptr(w_blocks), _ptr(bias32), _ptr(out32), c_int(nb), c_int(m),
+                                                        c_int(n), c_int(k), c_int(_DT[a_blocks.dtype]), self._stream()), "block-diagonal product (few tokens)")
+            return
+        for b in range(nb):
+            self.linear(a_blocks[b], w_blocks[b], None if bias32 is None else bias32[b], out32[b], "f32")
+
     # ---- recurrent mixers (recurrent.cu) -------------------------------------------------------------
     def delta_rule_scan(self, r32, k32, v32, a_logit32, w_logit32, state, ctx, o32, heads, d):
         """The generalized delta rule over every request's tokens in order, from and into ``state[slot]``
@@ -641,12 +659,13 @@ class Kernels:
         self._rows(x32, torch.float32, "rglru_scan x"); _need(softplus_lam32, torch.float32, "rglru_scan lam"); _need(state, torch.float32, "rglru_scan state")
         _need(out, None, "rglru_scan out")
         m, width = u32.shape
+        work = torch.empty((3, m, width), dtype=torch.float32, device=u32.device)      # decay, input and gelu per (token, channel)
         if tuple(gates32.shape) != (blocks, m, 2 * (width // blocks)) or tuple(state.shape[1:]) != (taps, width) \
                 or tuple(out.shape) != (m, width) or tuple(y_logit32.shape) != (m, width) or tuple(x32.shape) != (m, width):
             raise KernelError("rglru_scan: shapes do not fit")
         self._check(self._lib.nib_rglru_scan(
             _ptr(u32), _ptr(gates32), _ptr(y_logit32), c_int(y_logit32.stride(0)), _ptr(x32), c_int(x32.stride(0)),
-            _ptr(softplus_lam32), _ptr(state), _ptr(ctx.q_start), _ptr(ctx.state_slots), _ptr(out), c_int(m),
+            _ptr(softplus_lam32), _ptr(state), _ptr(ctx.q_start), _ptr(ctx.state_slots), _ptr(out), _ptr(work), c_int(m),
             c_int(ctx.host.num_requests), c_int(width), c_int(taps), c_int(blocks), c_int(_DT[out.dtype]), self._stream()), "rglru_scan")
 
     # ---- attention through a latent (latent_attention.cu) -------------------------------------------

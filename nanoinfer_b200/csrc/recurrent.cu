@@ -1,7 +1,8 @@
 // Recurrent mixers over a flat batch of requests: each request brings any number of tokens (a prompt's portion or
 // one decoded token), its state lives in 32-bit floats in a slot of a state tensor and is carried from step to step.
-// Every kernel walks a request's tokens in order with the same arithmetic per token whatever the cut, so a
-// position's result does not depend on how the request was cut into steps or on what else is in the batch.
+// The delta rule and the convolution walk a request's tokens in order with the same arithmetic per token whatever
+// the cut; the gated recurrence chains segments of the request's tokens, so its results depend on the cut by
+// rounding only. Nothing depends on what else is in the batch.
 // Which request owns which rows and which slot is read from device arrays (q_start, slots), so a captured graph
 // can replay the launches for other requests.
 //
@@ -48,25 +49,46 @@ delta_rule_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
         s[i] = (col_ok && ch < d) ? st[ch] : 0.f;
     }
     const size_t hoff = (size_t)head * d;
-    for (int c0 = 0; c0 < n_tok; c0 += TC) {
+    // A chunk's vectors are fetched into registers while the chunk before is being walked, then turned into decay,
+    // removal rate and unit key in shared memory: the walk never waits for global memory.
+    constexpr int PER = (TC * DP + DR_THREADS - 1) / DR_THREADS;        // (token, channel) pairs per thread
+    constexpr int PERV = (TC * DR_CV + DR_THREADS - 1) / DR_THREADS;
+    float f_k[PER], f_r[PER], f_a[PER], f_w[PER], f_v[PERV];
+    auto fetch = [&](int c0) {
         const int nc = min(TC, n_tok - c0);
-        __syncthreads();       // the chunk before has been read
-        for (int idx = tid; idx < TC * DP; idx += DR_THREADS) {
-            const int t = idx / DP, ch = idx % DP;
-            float kk = 0.f, rr = 0.f, ww = 0.f, aa = 0.f;
-            if (t < nc && ch < d) {
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int idx = tid + j * DR_THREADS, t = idx / DP, ch = idx % DP;
+            f_k[j] = f_r[j] = f_a[j] = f_w[j] = 0.f;
+            if (idx < TC * DP && t < nc && ch < d) {
                 const size_t row = (size_t)(t0 + c0 + t);
-                kk = k[row * ld + hoff + ch];
-                rr = r[row * ld + hoff + ch];
-                aa = sigmoidf_(a_logit[row * ld + hoff + ch]);
-                ww = expf(-0.60653065971263342f * sigmoidf_(w_logit[row * ldw + hoff + ch]));
+                f_k[j] = k[row * ld + hoff + ch];
+                f_r[j] = r[row * ld + hoff + ch];
+                f_a[j] = a_logit[row * ld + hoff + ch];
+                f_w[j] = w_logit[row * ldw + hoff + ch];
             }
-            s_k[t][ch] = kk; s_r[t][ch] = rr; s_w[t][ch] = ww; s_au[t][ch] = aa;
         }
-        for (int idx = tid; idx < TC * DR_CV; idx += DR_THREADS) {
-            const int t = idx / DR_CV, c = idx % DR_CV;
-            const int cc = blockIdx.x * DR_CV + c;
-            s_v[t][c] = (t < nc && cc < d) ? v[(size_t)(t0 + c0 + t) * ld + hoff + cc] : 0.f;
+#pragma unroll
+        for (int j = 0; j < PERV; ++j) {
+            const int idx = tid + j * DR_THREADS, t = idx / DR_CV, cc = blockIdx.x * DR_CV + idx % DR_CV;
+            f_v[j] = (idx < TC * DR_CV && t < nc && cc < d) ? v[(size_t)(t0 + c0 + t) * ld + hoff + cc] : 0.f;
+        }
+    };
+    auto stage = [&](int c0) {
+        const int nc = min(TC, n_tok - c0);
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int idx = tid + j * DR_THREADS, t = idx / DP, ch = idx % DP;
+            if (idx >= TC * DP) continue;
+            const bool live = t < nc && ch < d;
+            s_k[t][ch] = f_k[j]; s_r[t][ch] = f_r[j];
+            s_au[t][ch] = live ? sigmoidf_(f_a[j]) : 0.f;
+            s_w[t][ch] = live ? expf(-0.60653065971263342f * sigmoidf_(f_w[j])) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < PERV; ++j) {
+            const int idx = tid + j * DR_THREADS;
+            if (idx < TC * DR_CV) s_v[idx / DR_CV][idx % DR_CV] = f_v[j];
         }
         __syncthreads();
         // the unit key: one warp per token, lanes over the channels, a fixed order of additions
@@ -82,6 +104,13 @@ delta_rule_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
             }
         }
         __syncthreads();
+    };
+    if (n_tok > 0) fetch(0);
+    for (int c0 = 0; c0 < n_tok; c0 += TC) {
+        const int nc = min(TC, n_tok - c0);
+        __syncthreads();       // the chunk before has been walked
+        stage(c0);
+        if (c0 + TC < n_tok) fetch(c0 + TC);
         for (int t = 0; t < nc; ++t) {
             const float* pu = &s_u[t][lane8 * KR];
             const float* pw = &s_w[t][lane8 * KR];
@@ -185,41 +214,92 @@ NIB_API int nib_causal_conv(const float* x, int ldx, const float* w, const float
 }
 
 // ---------------------------------------------------------------------------------- gated linear recurrence
-// One thread per (request, channel) walks the request's tokens. gates: [blocks, tokens, 2 * bw] floats, the
-// recurrence gate's logits in the first bw columns of a block's rows and the input gate's in the last bw.
-// y_logit: the other branch before its gelu, row stride ldy. x: the convolution's inputs (row stride ldx), from
-// which the history rows of the state are renewed. state row 0 is S, rows 1.. the history.
+// Two kernels. The first is element-wise over (token, channel): from the gate logits (gates: [blocks, tokens,
+// 2 * bw] floats, the recurrence gate's logits in the first bw columns of a block's rows and the input gate's in the
+// last bw), u and the other branch's logits it writes a = exp(-8 r softplus(lam)), b = sqrt(1 - a^2) (i u) and
+// g = gelu_tanh(y) into work[0], work[1], work[2] ([3, tokens, width] floats). The second walks S <- a S + b:
+// a block owns 32 channels of one request (a lane per channel), its warps take consecutive segments of the
+// request's tokens; each warp first composes its segment into (product of a, end state from zero), the segments
+// are chained in order from the request's state, then each warp walks its segment again from its true entry state
+// and writes S * g. Loads are issued eight tokens ahead. State row 0 is S, rows 1.. the last taps-1 inputs x of the
+// convolution (row stride ldx), renewed here.
 constexpr int LRU_MAX_TAPS = 16;
+constexpr int LRU_WARPS = 16;
+constexpr int LRU_AHEAD = 8;
+
+__global__ void rglru_gate_kernel(const float* __restrict__ u32, const float* __restrict__ gates, const float* __restrict__ y_logit,
+                                  int ldy, const float* __restrict__ softplus_lam, float* __restrict__ work, int tokens, int width,
+                                  int blocks) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long n = (long long)tokens * width;
+    if (i >= n) return;
+    const int t = (int)(i / width), c = (int)(i % width);
+    const int bw = width / blocks, b = c / bw, cb = c % bw;
+    const float* g = gates + ((size_t)b * tokens + t) * 2 * bw + cb;
+    const float rg = sigmoidf_(g[0]), ig = sigmoidf_(g[bw]);
+    const float log_a = -8.0f * rg * softplus_lam[c];
+    work[i] = expf(log_a);
+    work[n + i] = sqrtf(fmaxf(0.f, -expm1f(2.0f * log_a))) * (ig * u32[i]);      // sqrt(1 - a^2) (i u)
+    const float z = y_logit[(size_t)t * ldy + c];
+    work[2 * n + i] = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
 
 template <typename T>
-__global__ void __launch_bounds__(128)
-rglru_scan_kernel(const float* __restrict__ u32, const float* __restrict__ gates, const float* __restrict__ y_logit, int ldy,
-                  const float* __restrict__ x, int ldx, const float* __restrict__ softplus_lam, float* __restrict__ state,
-                  const int* __restrict__ q_start, const int* __restrict__ slots, T* __restrict__ out, int tokens, int width,
-                  int taps, int blocks) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= width) return;
+__global__ void __launch_bounds__(LRU_WARPS * 32)
+rglru_scan_kernel(const float* __restrict__ work, const float* __restrict__ x, int ldx, float* __restrict__ state,
+                  const int* __restrict__ q_start, const int* __restrict__ slots, T* __restrict__ out, int tokens, int width, int taps) {
+    __shared__ float s_a[LRU_WARPS][32], s_b[LRU_WARPS][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane;
+    const bool live = c < width;
     const int req = blockIdx.y;
     const int t0 = q_start[req], n = q_start[req + 1] - t0;
     float* st = state + (size_t)slots[req] * taps * width;
-    const int bw = width / blocks, b = c / bw, cb = c % bw;
-    const float* g = gates + ((size_t)b * tokens) * 2 * bw + cb;
-    const float sp = softplus_lam[c];
-    float S = st[c];
-#pragma unroll 4
-    for (int t = 0; t < n; ++t) {
-        const size_t row = (size_t)(t0 + t);
-        const float rg = sigmoidf_(g[row * 2 * bw]), ig = sigmoidf_(g[row * 2 * bw + bw]);
-        const float log_a = -8.0f * rg * sp;
-        const float a = expf(log_a);
-        const float mult = sqrtf(fmaxf(0.f, -expm1f(2.0f * log_a)));      // sqrt(1 - a^2)
-        S = fmaf(a, S, mult * (ig * u32[row * width + c]));
-        const float z = y_logit[row * ldy + c];
-        const float ge = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-        Elem<T>::store(out + row * width + c, S * ge);
+    const size_t plane = (size_t)tokens * width;
+    const float* pa = work + (size_t)t0 * width + c;
+    const float* pb = pa + plane;
+    const float* pg = pb + plane;
+    const int seg = (n + LRU_WARPS - 1) / LRU_WARPS;
+    const int lo = min(n, warp * seg), hi = min(n, lo + seg);
+    // pass 1: the segment as one affine map S -> A S + B
+    float A = 1.f, B = 0.f;
+    if (live) {
+        for (int t = lo; t < hi; t += LRU_AHEAD) {
+            float av[LRU_AHEAD], bv[LRU_AHEAD];
+#pragma unroll
+            for (int j = 0; j < LRU_AHEAD; ++j) {
+                const bool in = t + j < hi;
+                av[j] = in ? pa[(size_t)(t + j) * width] : 1.f;
+                bv[j] = in ? pb[(size_t)(t + j) * width] : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < LRU_AHEAD; ++j) { B = fmaf(av[j], B, bv[j]); A *= av[j]; }
+        }
     }
+    s_a[warp][lane] = A; s_b[warp][lane] = B;
+    __syncthreads();
+    if (!live) return;
+    float S = st[c];
+    for (int w = 0; w < warp; ++w) S = fmaf(s_a[w][lane], S, s_b[w][lane]);
+    // pass 2: the segment again from its entry state
+    for (int t = lo; t < hi; t += LRU_AHEAD) {
+        float av[LRU_AHEAD], bv[LRU_AHEAD], gv[LRU_AHEAD];
+#pragma unroll
+        for (int j = 0; j < LRU_AHEAD; ++j) {
+            const bool in = t + j < hi;
+            av[j] = in ? pa[(size_t)(t + j) * width] : 1.f;
+            bv[j] = in ? pb[(size_t)(t + j) * width] : 0.f;
+            gv[j] = in ? pg[(size_t)(t + j) * width] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < LRU_AHEAD; ++j) {
+            S = fmaf(av[j], S, bv[j]);
+            if (t + j < hi) Elem<T>::store(out + (size_t)(t0 + t + j) * width + c, S * gv[j]);
+        }
+    }
+    if (warp != LRU_WARPS - 1) return;
+    // the last warp leaves with the request's new state (empty segments are the identity map)
     st[c] = S;
-    // the last taps-1 inputs: from this step's rows where there are enough, else shifted up from the old history
     float keep[LRU_MAX_TAPS];
     for (int j = 0; j < taps - 1; ++j) {
         const int src = n - (taps - 1) + j;
@@ -228,21 +308,23 @@ rglru_scan_kernel(const float* __restrict__ u32, const float* __restrict__ gates
     for (int j = 0; j < taps - 1; ++j) st[(size_t)(1 + j) * width + c] = keep[j];
 }
 
+// work: [3, tokens, width] floats of scratch.
 NIB_API int nib_rglru_scan(const float* u32, const float* gates, const float* y_logit, int ldy, const float* x, int ldx,
-                           const float* softplus_lam, float* state, const int* q_start, const int* slots, void* out,
+                           const float* softplus_lam, float* state, const int* q_start, const int* slots, void* out, float* work,
                            int tokens, int requests, int width, int taps, int blocks, int dtype, cudaStream_t stream) {
     NIB_REQUIRE(requests >= 0 && width > 0 && taps >= 1 && taps <= LRU_MAX_TAPS && blocks >= 1 && width % blocks == 0,
                 "rglru_scan: bad sizes (width %d, taps %d of at most %d, blocks %d)", width, taps, LRU_MAX_TAPS, blocks);
+    NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "rglru_scan: unknown dtype %d", dtype);
     if (requests == 0 || tokens == 0) return 0;
-    const dim3 grid(ceil_div(width, 128), requests);
+    rglru_gate_kernel<<<ceil_div((long long)tokens * width, 256), 256, 0, stream>>>(u32, gates, y_logit, ldy, softplus_lam, work,
+                                                                                    tokens, width, blocks);
+    NIB_LAUNCH_CHECK();
+    const dim3 grid(ceil_div(width, 32), requests);
     if (dtype == NIB_F32)
-        rglru_scan_kernel<float><<<grid, 128, 0, stream>>>(u32, gates, y_logit, ldy, x, ldx, softplus_lam, state, q_start, slots,
-                                                           (float*)out, tokens, width, taps, blocks);
-    else if (dtype == NIB_BF16)
-        rglru_scan_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(u32, gates, y_logit, ldy, x, ldx, softplus_lam, state, q_start,
-                                                                   slots, (__nv_bfloat16*)out, tokens, width, taps, blocks);
+        rglru_scan_kernel<float><<<grid, LRU_WARPS * 32, 0, stream>>>(work, x, ldx, state, q_start, slots, (float*)out, tokens, width, taps);
     else
-        NIB_REQUIRE(false, "rglru_scan: unknown dtype %d", dtype);
+        rglru_scan_kernel<__nv_bfloat16><<<grid, LRU_WARPS * 32, 0, stream>>>(work, x, ldx, state, q_start, slots, (__nv_bfloat16*)out,
+                                                                              tokens, width, taps);
     NIB_LAUNCH_CHECK();
     return 0;
 }

@@ -98,6 +98,17 @@ def test_unary_and_head_norm_gate(ops, dtype):
     assert_close(got, ref, dtype, "head_norm_gate")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("blocks,m,n,k", [(1, 1, 8, 8), (3, 5, 32, 16), (4, 16, 256, 128), (2, 40, 64, 32), (4, 300, 128, 64)])
+def test_block_diagonal_product(ops, dtype, blocks, m, n, k):
+    a, w, bias = rnd(blocks, m, k, seed=1).to(dtype), rnd(blocks, n, k, seed=2, scale=k ** -0.5).to(dtype), rnd(blocks, n, seed=3)
+    out = torch.empty(blocks, m, n, device=DEV)
+    ops.block_diag_linear(a, w, bias, out)
+    ref = torch.empty(blocks, m, n)
+    TorchOps().block_diag_linear(a.cpu(), w.cpu(), bias.cpu(), ref)
+    assert_close(out, ref, torch.float32, "block-diagonal product")
+
+
 # ------------------------------------------------------------------------------------------ generalized delta rule
 def _delta_inputs(m, heads, d, seed):
     wide = rnd(m, 4 * heads * d + 3, seed=seed)

@@ -118,6 +118,12 @@ class TorchOps:
         o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps)
         out.copy_((o.reshape(m, heads * d) * gain32.double() * torch.sigmoid(gate32.double())).to(out.dtype))
 
+    def block_diag_linear(self, a_blocks, w_blocks, bias32, out32):
+        y = torch.einsum("bmk,bnk->bmn", a_blocks.double(), w_blocks.double())
+        if bias32 is not None:
+            y = y + bias32.double()[:, None, :]
+        out32.copy_(y.to(torch.float32))
+
     # ---- recurrent mixers of recurrent.cu -----------------------------------------------------------
     def delta_rule_scan(self, r32, k32, v32, a_logit32, w_logit32, state, ctx, o32, heads, d):
         import math
