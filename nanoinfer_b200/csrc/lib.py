@@ -83,7 +83,7 @@ class Kernels:
                      "nib_gemm_tc_qkv_supported", "nib_poly_norm", "nib_depth_mix", "nib_unary", "nib_head_norm_gate",
                      "nib_delta_rule_scan", "nib_causal_conv", "nib_rglru_scan", "nib_latent_store", "nib_latent_query",
                      "nib_latent_attention", "nib_latent_value", "nib_latent_attention_mma", "nib_latent_attention_mma_supported",
-                     "nib_latent_attention_mma_qwidth", "nib_block_diag_smallm"):
+                     "nib_latent_attention_mma_qwidth", "nib_block_diag_smallm", "nib_rmsnorm_pair", "nib_rmsnorm_pair_supported"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -563,6 +563,21 @@ class Kernels:
         if t.dim() != 2 or t.stride(1) != 1:
             raise KernelError(f"{what}: rows must be dense")
 
+    def rmsnorm_pair(self, x32, gain_a32, gain_b32, eps, out_a, out_b):
+        """Two RMS norms of the same rows with different gains (the two branches of a parallel block): the rows are read
+        and their statistic computed once where the width allows, else one after the other."""
+        if self._lib.nib_rmsnorm_pair_supported(c_int(x32.shape[1])) != 1:
+            self.rmsnorm(x32, gain_a32, eps, out_a)
+            self.rmsnorm(x32, gain_b32, eps, out_b)
+            return
+        _need(x32, torch.float32, "rmsnorm_pair x"); _need(gain_a32, torch.float32, "rmsnorm_pair gain"); _need(gain_b32, torch.float32, "rmsnorm_pair gain")
+        _need(out_a, None, "rmsnorm_pair out"); _need(out_b, out_a.dtype, "rmsnorm_pair out")
+        n, hidden = x32.shape
+        if tuple(out_a.shape) != (n, hidden) or tuple(out_b.shape) != (n, hidden) or gain_a32.numel() != hidden or gain_b32.numel() != hidden:
+            raise KernelError("rmsnorm_pair: shapes do not fit")
+        self._check(self._lib.nib_rmsnorm_pair(_ptr(x32), _ptr(gain_a32), _ptr(gain_b32), _ptr(out_a), _ptr(out_b), c_int(n), c_int(hidden),
+                                               c_float(eps), c_int(_DT[out_a.dtype]), self._stream()), "rmsnorm (two gains)")
+
     def poly_norm(self, z32, coef32, eps, out):
         """out = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 per row, N(y) = y / sqrt(mean(y^2) + eps); coef32 = (c0..c3)."""
         self._rows(z32, torch.float32, "poly_norm z"); self._rows(out, None, "poly_norm out")
@@ -631,10 +646,11 @@ class Kernels:
         if any(tuple(t.shape) != (m, heads * d) for t in (r32, k32, v32, a_logit32, w_logit32, o32)) \
                 or len({t.stride(0) for t in (r32, k32, v32, a_logit32)}) != 1 or tuple(state.shape[1:]) != (heads, d, d):
             raise KernelError("delta_rule_scan: shapes do not fit")
+        work = torch.empty((3, m, heads * d), dtype=torch.float32, device=r32.device)      # decay, unit key, removal per (token, channel)
         self._check(self._lib.nib_delta_rule_scan(
             _ptr(r32), _ptr(k32), _ptr(v32), _ptr(a_logit32), c_int(r32.stride(0)), _ptr(w_logit32), c_int(w_logit32.stride(0)),
-            _ptr(state), _ptr(ctx.q_start), _ptr(ctx.state_slots), _ptr(o32), c_int(o32.stride(0)), c_int(ctx.host.num_requests),
-            c_int(heads), c_int(d), self._stream()), "delta_rule_scan")
+            _ptr(state), _ptr(ctx.q_start), _ptr(ctx.state_slots), _ptr(o32), c_int(o32.stride(0)), _ptr(work), c_int(m),
+            c_int(ctx.host.num_requests), c_int(heads), c_int(d), self._stream()), "delta_rule_scan")
 
     def causal_conv(self, x32, w32, bias32, state, hist_row0, ctx, u32, u_blocks, taps, blocks):
         """u = bias + sum_j w[:, j] * x[t - (taps-1-j)] per channel within each request; inputs before the step's first

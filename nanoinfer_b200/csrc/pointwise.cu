@@ -70,10 +70,30 @@ __global__ void depth_mix_kernel(float* __restrict__ hist, float* __restrict__ x
     x[i] = fmaf(coef[n - 1], newest, acc);
 }
 
+// the same with four elements a thread (n_elem a multiple of 4, 16-byte aligned streams)
+__global__ void depth_mix4_kernel(float4* __restrict__ hist, float4* __restrict__ x, const float* __restrict__ coef, int n,
+                                  long long n_vec) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_vec) return;
+    const float4 newest = x[i];
+    hist[(size_t)(n - 1) * n_vec + i] = newest;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < n - 1; ++j) {
+        const float c = coef[j];
+        const float4 h = hist[(size_t)j * n_vec + i];
+        acc.x = fmaf(c, h.x, acc.x); acc.y = fmaf(c, h.y, acc.y); acc.z = fmaf(c, h.z, acc.z); acc.w = fmaf(c, h.w, acc.w);
+    }
+    const float c = coef[n - 1];
+    x[i] = make_float4(fmaf(c, newest.x, acc.x), fmaf(c, newest.y, acc.y), fmaf(c, newest.z, acc.z), fmaf(c, newest.w, acc.w));
+}
+
 NIB_API int nib_depth_mix(float* hist, float* x, const float* coef, int n, long long n_elem, cudaStream_t stream) {
     NIB_REQUIRE(n >= 1 && n_elem >= 0, "depth_mix: bad sizes n=%d", n);
     if (n_elem == 0) return 0;
-    depth_mix_kernel<<<ceil_div(n_elem, 256), 256, 0, stream>>>(hist, x, coef, n, n_elem);
+    if (n_elem % 4 == 0 && (((uintptr_t)hist | (uintptr_t)x) & 15) == 0)
+        depth_mix4_kernel<<<ceil_div(n_elem / 4, 256), 256, 0, stream>>>((float4*)hist, (float4*)x, coef, n, n_elem / 4);
+    else
+        depth_mix_kernel<<<ceil_div(n_elem, 256), 256, 0, stream>>>(hist, x, coef, n, n_elem);
     NIB_LAUNCH_CHECK();
     return 0;
 }
@@ -134,6 +154,68 @@ NIB_API int nib_head_norm_gate(const float* o, int ldo, const float* gate, int l
     if (dtype == NIB_F32) head_norm_gate_kernel<float><<<blocks, 128, 0, stream>>>(o, ldo, gate, ldg, gain, (float*)out, ld_out, tokens, heads, d, eps);
     else if (dtype == NIB_BF16) head_norm_gate_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(o, ldo, gate, ldg, gain, (__nv_bfloat16*)out, ld_out, tokens, heads, d, eps);
     else NIB_REQUIRE(false, "head_norm_gate: unknown dtype %d", dtype);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------- two RMS norms of one row
+// out_a = x / rms(x) * gain_a and out_b = x / rms(x) * gain_b: the two branches of a parallel block read the same
+// stream, so the row is read and its statistic computed once. One warp per row, the row in registers (NV float4 a
+// lane); widths that are multiples of 4 up to 128 * NV.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_pair_kernel(const float* __restrict__ x, const float* __restrict__ gain_a, const float* __restrict__ gain_b,
+                    T* __restrict__ out_a, T* __restrict__ out_b, int n_rows, int hidden, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const int n4 = hidden >> 2;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)r * hidden);
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        v[i] = c < n4 ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+        ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+    }
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        if (c >= n4) continue;
+        const float4 ga = __ldg(reinterpret_cast<const float4*>(gain_a) + c), gb = __ldg(reinterpret_cast<const float4*>(gain_b) + c);
+        const float sx = v[i].x * scale, sy = v[i].y * scale, sz = v[i].z * scale, sw = v[i].w * scale;
+        T* oa = out_a + (size_t)r * hidden + 4 * c;
+        T* ob = out_b + (size_t)r * hidden + 4 * c;
+        Elem<T>::store(oa, sx * ga.x); Elem<T>::store(oa + 1, sy * ga.y); Elem<T>::store(oa + 2, sz * ga.z); Elem<T>::store(oa + 3, sw * ga.w);
+        Elem<T>::store(ob, sx * gb.x); Elem<T>::store(ob + 1, sy * gb.y); Elem<T>::store(ob + 2, sz * gb.z); Elem<T>::store(ob + 3, sw * gb.w);
+    }
+}
+
+// 1 if nib_rmsnorm_pair takes rows of this width.
+NIB_API int nib_rmsnorm_pair_supported(int hidden) { return (hidden % 4 == 0 && hidden > 0 && hidden <= 4096) ? 1 : 0; }
+
+NIB_API int nib_rmsnorm_pair(const float* x, const float* gain_a, const float* gain_b, void* out_a, void* out_b, int n_rows,
+                             int hidden, float eps, int dtype, cudaStream_t stream) {
+    NIB_REQUIRE(n_rows >= 0 && nib_rmsnorm_pair_supported(hidden) == 1, "rmsnorm_pair: bad sizes rows=%d hidden=%d", n_rows, hidden);
+    NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "rmsnorm_pair: unknown dtype %d", dtype);
+    NIB_REQUIRE((((uintptr_t)x | (uintptr_t)gain_a | (uintptr_t)gain_b) & 15) == 0, "rmsnorm_pair: rows and gains must start on 16-byte boundaries");
+    if (n_rows == 0) return 0;
+    const int warps = n_rows >= 8 ? 8 : n_rows;
+    const dim3 grid(ceil_div(n_rows, warps)), block(32 * warps);
+#define NIB_RP(T, NV) rmsnorm_pair_kernel<T, NV><<<grid, block, 0, stream>>>(x, gain_a, gain_b, (T*)out_a, (T*)out_b, n_rows, hidden, eps)
+    if (dtype == NIB_F32) {
+        if (hidden <= 1024) NIB_RP(float, 8); else if (hidden <= 2048) NIB_RP(float, 16); else NIB_RP(float, 32);
+    } else {
+        if (hidden <= 1024) NIB_RP(__nv_bfloat16, 8); else if (hidden <= 2048) NIB_RP(__nv_bfloat16, 16); else NIB_RP(__nv_bfloat16, 32);
+    }
+#undef NIB_RP
     NIB_LAUNCH_CHECK();
     return 0;
 }

@@ -9,9 +9,10 @@
 //  * generalized delta rule: per head a matrix state S [key channel x value channel];
 //      S <- diag(w) S - (a * u)(u^T S) + k v^T   (both products read the old S),   o = S^T r
 //    with w = exp(-exp(-1/2) sigmoid(w_logit)), a = sigmoid(a_logit), u = k / sqrt(sum k^2 + 1e-6).
-//    The value columns of S are independent of one another: a block owns 16 columns of one head of one request,
-//    eight lanes share a column (each holds a slice of the key channels in registers), the token's vectors are
-//    staged in shared memory a chunk of tokens at a time.
+//    Decay, unit key and removal are computed for all tokens in parallel first. The value columns of S are
+//    independent of one another: a block owns 16 columns of one head of one request, eight lanes share a column
+//    (each holds a slice of the key channels in registers), the tokens' vectors are staged in shared memory a chunk
+//    at a time; what a token costs is the chain projection -> butterfly over the eight lanes -> update.
 //  * short causal convolution per channel with its last taps-1 inputs kept in the state;
 //  * real-gated linear recurrent unit: S <- a S + sqrt(1 - a^2) (i * u), a = exp(-8 r softplus(lam)), r and i
 //    sigmoids of block-diagonal products of u (computed by the matrix kernels before), output S * gelu(y).
@@ -20,19 +21,45 @@
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 // ---------------------------------------------------------------------------------- generalized delta rule
+// Two kernels. The first is parallel over (token, head), a warp each: decay w, unit key u and a * u from the logits
+// and the key, into work[0], work[1], work[2] ([3, tokens, heads*d] floats). The second walks the tokens.
 constexpr int DR_CV = 16;      // value columns per block
 constexpr int DR_LPC = 8;      // lanes per column
 constexpr int DR_THREADS = DR_CV * DR_LPC;
 
+__global__ void __launch_bounds__(128)
+delta_rule_prepare_kernel(const float* __restrict__ k, const float* __restrict__ a_logit, int ld, const float* __restrict__ w_logit,
+                          int ldw, float* __restrict__ work, int tokens, int heads, int d) {
+    const long long wid = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)tokens * heads) return;
+    const int t = (int)(wid / heads), h = (int)(wid % heads);
+    const size_t in = (size_t)t * ld + (size_t)h * d, inw = (size_t)t * ldw + (size_t)h * d;
+    const size_t plane = (size_t)tokens * heads * d, out = ((size_t)t * heads + h) * d;
+    float ss = 0.f;
+    for (int ch = lane; ch < d; ch += 32) ss = fmaf(k[in + ch], k[in + ch], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss + 1e-6f);
+    for (int ch = lane; ch < d; ch += 32) {
+        const float u = k[in + ch] * inv;
+        work[out + ch] = expf(-0.60653065971263342f * sigmoidf_(w_logit[inw + ch]));      // exp(-exp(-1/2) sigmoid)
+        work[plane + out + ch] = u;
+        work[2 * plane + out + ch] = sigmoidf_(a_logit[in + ch]) * u;
+    }
+}
+
 template <int KR>
 __global__ void __launch_bounds__(DR_THREADS)
-delta_rule_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
-                       const float* __restrict__ a_logit, int ld, const float* __restrict__ w_logit, int ldw,
-                       float* __restrict__ state, const int* __restrict__ q_start, const int* __restrict__ slots,
-                       float* __restrict__ o, int ldo, int heads, int d) {
+delta_rule_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v, int ld,
+                       const float* __restrict__ work, float* __restrict__ state, const int* __restrict__ q_start,
+                       const int* __restrict__ slots, float* __restrict__ o, int ldo, int tokens, int heads, int d) {
+    constexpr bool VEC = KR % 4 == 0;
+    // a lane's slice, padded to an odd number of 16-byte units so that the eight lanes' 16-byte loads fall into distinct banks
+    constexpr int KRP = (VEC && (KR / 4) % 2 == 0) ? KR + 4 : KR;
     constexpr int DP = DR_LPC * KR;                 // key channels with padding
-    constexpr int TC = DP <= 128 ? 16 : 8;          // tokens staged at a time
-    __shared__ float s_w[TC][DP], s_au[TC][DP], s_u[TC][DP], s_k[TC][DP], s_r[TC][DP];
+    constexpr int DPP = DR_LPC * KRP;
+    constexpr int TC = DPP <= 96 ? 16 : 8;          // tokens staged at a time
+    __shared__ __align__(16) float s_w[TC][DPP], s_au[TC][DPP], s_u[TC][DPP], s_k[TC][DPP], s_r[TC][DPP];
     __shared__ float s_v[TC][DR_CV];
     const int tid = threadIdx.x, lane8 = tid % DR_LPC, col_local = tid / DR_LPC;
     const int head = blockIdx.y, req = blockIdx.z;
@@ -48,24 +75,25 @@ delta_rule_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
         const int ch = lane8 * KR + i;
         s[i] = (col_ok && ch < d) ? st[ch] : 0.f;
     }
-    const size_t hoff = (size_t)head * d;
-    // A chunk's vectors are fetched into registers while the chunk before is being walked, then turned into decay,
-    // removal rate and unit key in shared memory: the walk never waits for global memory.
+    const size_t hoff = (size_t)head * d, n_all = (size_t)heads * d, plane = (size_t)tokens * n_all;
+    // A chunk's vectors are fetched into registers while the chunk before is being walked: the walk never waits
+    // for global memory.
     constexpr int PER = (TC * DP + DR_THREADS - 1) / DR_THREADS;        // (token, channel) pairs per thread
     constexpr int PERV = (TC * DR_CV + DR_THREADS - 1) / DR_THREADS;
-    float f_k[PER], f_r[PER], f_a[PER], f_w[PER], f_v[PERV];
+    float f_k[PER], f_r[PER], f_a[PER], f_w[PER], f_u[PER], f_v[PERV];
     auto fetch = [&](int c0) {
         const int nc = min(TC, n_tok - c0);
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
             const int idx = tid + j * DR_THREADS, t = idx / DP, ch = idx % DP;
-            f_k[j] = f_r[j] = f_a[j] = f_w[j] = 0.f;
+            f_k[j] = f_r[j] = f_a[j] = f_w[j] = f_u[j] = 0.f;
             if (idx < TC * DP && t < nc && ch < d) {
                 const size_t row = (size_t)(t0 + c0 + t);
                 f_k[j] = k[row * ld + hoff + ch];
                 f_r[j] = r[row * ld + hoff + ch];
-                f_a[j] = a_logit[row * ld + hoff + ch];
-                f_w[j] = w_logit[row * ldw + hoff + ch];
+                f_w[j] = work[row * n_all + hoff + ch];
+                f_u[j] = work[plane + row * n_all + hoff + ch];
+                f_a[j] = work[2 * plane + row * n_all + hoff + ch];
             }
         }
 #pragma unroll
@@ -74,16 +102,13 @@ delta_rule_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
             f_v[j] = (idx < TC * DR_CV && t < nc && cc < d) ? v[(size_t)(t0 + c0 + t) * ld + hoff + cc] : 0.f;
         }
     };
-    auto stage = [&](int c0) {
-        const int nc = min(TC, n_tok - c0);
+    auto stage = [&]() {
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
             const int idx = tid + j * DR_THREADS, t = idx / DP, ch = idx % DP;
             if (idx >= TC * DP) continue;
-            const bool live = t < nc && ch < d;
-            s_k[t][ch] = f_k[j]; s_r[t][ch] = f_r[j];
-            s_au[t][ch] = live ? sigmoidf_(f_a[j]) : 0.f;
-            s_w[t][ch] = live ? expf(-0.60653065971263342f * sigmoidf_(f_w[j])) : 0.f;
+            const int at = (ch / KR) * KRP + ch % KR;
+            s_k[t][at] = f_k[j]; s_r[t][at] = f_r[j]; s_w[t][at] = f_w[j]; s_u[t][at] = f_u[j]; s_au[t][at] = f_a[j];
         }
 #pragma unroll
         for (int j = 0; j < PERV; ++j) {
@@ -91,50 +116,61 @@ delta_rule_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
             if (idx < TC * DR_CV) s_v[idx / DR_CV][idx % DR_CV] = f_v[j];
         }
         __syncthreads();
-        // the unit key: one warp per token, lanes over the channels, a fixed order of additions
-        for (int t = tid >> 5; t < nc; t += DR_THREADS / 32) {
-            float ss = 0.f;
-            for (int ch = tid & 31; ch < DP; ch += 32) ss = fmaf(s_k[t][ch], s_k[t][ch], ss);
-            ss = warp_sum(ss);
-            const float inv = 1.0f / sqrtf(ss + 1e-6f);
-            for (int ch = tid & 31; ch < DP; ch += 32) {
-                const float u = s_k[t][ch] * inv;
-                s_u[t][ch] = u;
-                s_au[t][ch] *= u;
+    };
+    auto take = [&](float (&dst)[KR], const float* src) {
+        if constexpr (VEC) {
+#pragma unroll
+            for (int i = 0; i < KR / 4; ++i) {
+                const float4 x = reinterpret_cast<const float4*>(src)[i];
+                dst[4 * i] = x.x; dst[4 * i + 1] = x.y; dst[4 * i + 2] = x.z; dst[4 * i + 3] = x.w;
             }
+        } else {
+#pragma unroll
+            for (int i = 0; i < KR; ++i) dst[i] = src[i];
         }
-        __syncthreads();
     };
     if (n_tok > 0) fetch(0);
+    float out_prev = 0.f;       // the token before's output, summed over the lanes while this token's projection is
+    long long prev_at = -1;
     for (int c0 = 0; c0 < n_tok; c0 += TC) {
         const int nc = min(TC, n_tok - c0);
         __syncthreads();       // the chunk before has been walked
-        stage(c0);
+        stage();
         if (c0 + TC < n_tok) fetch(c0 + TC);
         for (int t = 0; t < nc; ++t) {
-            const float* pu = &s_u[t][lane8 * KR];
-            const float* pw = &s_w[t][lane8 * KR];
-            const float* pa = &s_au[t][lane8 * KR];
-            const float* pk = &s_k[t][lane8 * KR];
-            const float* pr = &s_r[t][lane8 * KR];
-            float proj = 0.f;
-#pragma unroll
-            for (int i = 0; i < KR; ++i) proj = fmaf(pu[i], s[i], proj);
-            proj += __shfl_xor_sync(0xffffffffu, proj, 1);
-            proj += __shfl_xor_sync(0xffffffffu, proj, 2);
-            proj += __shfl_xor_sync(0xffffffffu, proj, 4);
+            float cu[KR], cw[KR], ca[KR], ck[KR], cr[KR];
+            take(cu, &s_u[t][lane8 * KRP]);
+            take(cw, &s_w[t][lane8 * KRP]);
+            take(ca, &s_au[t][lane8 * KRP]);
+            take(ck, &s_k[t][lane8 * KRP]);
+            take(cr, &s_r[t][lane8 * KRP]);
             const float vj = s_v[t][col_local];
-            float out = 0.f;
+            float p0 = 0.f, p1 = 0.f;
 #pragma unroll
             for (int i = 0; i < KR; ++i) {
-                s[i] = fmaf(pk[i], vj, fmaf(-pa[i], proj, pw[i] * s[i]));
-                out = fmaf(s[i], pr[i], out);
+                if (i & 1) p1 = fmaf(cu[i], s[i], p1); else p0 = fmaf(cu[i], s[i], p0);
             }
-            out += __shfl_xor_sync(0xffffffffu, out, 1);
-            out += __shfl_xor_sync(0xffffffffu, out, 2);
-            out += __shfl_xor_sync(0xffffffffu, out, 4);
-            if (lane8 == 0 && col_ok) o[(size_t)(t0 + c0 + t) * ldo + hoff + col] = out;
+            float proj = p0 + p1;
+#pragma unroll
+            for (int m = 1; m < DR_LPC; m <<= 1) {      // two independent butterflies side by side
+                const float x = __shfl_xor_sync(0xffffffffu, proj, m), y = __shfl_xor_sync(0xffffffffu, out_prev, m);
+                proj += x; out_prev += y;
+            }
+            if (prev_at >= 0 && lane8 == 0 && col_ok) o[prev_at] = out_prev;
+            float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < KR; ++i) {
+                s[i] = fmaf(ck[i], vj, fmaf(-ca[i], proj, cw[i] * s[i]));
+                if (i & 1) o1 = fmaf(s[i], cr[i], o1); else o0 = fmaf(s[i], cr[i], o0);
+            }
+            out_prev = o0 + o1;
+            prev_at = (long long)(t0 + c0 + t) * ldo + hoff + col;
         }
+    }
+    if (prev_at >= 0) {
+#pragma unroll
+        for (int m = 1; m < DR_LPC; m <<= 1) out_prev += __shfl_xor_sync(0xffffffffu, out_prev, m);
+        if (lane8 == 0 && col_ok) o[prev_at] = out_prev;
     }
     if (col_ok) {
 #pragma unroll
@@ -146,20 +182,23 @@ delta_rule_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
 }
 
 // r, k, v, a_logit: [tokens, heads*d] floats with row stride ld; w_logit likewise with row stride ldw;
-// state: [slots, heads, d, d] floats; o: [tokens, heads*d] floats with row stride ldo.
+// state: [slots, heads, d, d] floats; o: [tokens, heads*d] floats with row stride ldo; work: [3, tokens, heads*d]
+// floats of scratch.
 NIB_API int nib_delta_rule_scan(const float* r, const float* k, const float* v, const float* a_logit, int ld,
                                 const float* w_logit, int ldw, float* state, const int* q_start, const int* slots,
-                                float* o, int ldo, int requests, int heads, int d, cudaStream_t stream) {
+                                float* o, int ldo, float* work, int tokens, int requests, int heads, int d, cudaStream_t stream) {
     NIB_REQUIRE(requests >= 0 && heads > 0 && d > 0 && d <= 256, "delta_rule_scan: head size %d is outside 1..256", d);
-    if (requests == 0) return 0;
+    if (requests == 0 || tokens == 0) return 0;
+    delta_rule_prepare_kernel<<<ceil_div((long long)tokens * heads, 4), 128, 0, stream>>>(k, a_logit, ld, w_logit, ldw, work, tokens, heads, d);
+    NIB_LAUNCH_CHECK();
     const dim3 grid(ceil_div(d, DR_CV), heads, requests);
     const int kr = ceil_div(d, DR_LPC);
-#define NIB_DR(KR)                                                                                                      \
-    if (kr <= KR) {                                                                                                     \
-        delta_rule_scan_kernel<KR><<<grid, DR_THREADS, 0, stream>>>(r, k, v, a_logit, ld, w_logit, ldw, state, q_start, \
-                                                                    slots, o, ldo, heads, d);                          \
-        NIB_LAUNCH_CHECK();                                                                                             \
-        return 0;                                                                                                       \
+#define NIB_DR(KR)                                                                                                         \
+    if (kr <= KR) {                                                                                                        \
+        delta_rule_scan_kernel<KR><<<grid, DR_THREADS, 0, stream>>>(r, k, v, ld, work, state, q_start, slots, o, ldo, tokens, \
+                                                                    heads, d);                                             \
+        NIB_LAUNCH_CHECK();                                                                                                \
+        return 0;                                                                                                          \
     }
     NIB_DR(1) NIB_DR(2) NIB_DR(3) NIB_DR(4) NIB_DR(6) NIB_DR(8) NIB_DR(12) NIB_DR(16) NIB_DR(24) NIB_DR(32)
 #undef NIB_DR

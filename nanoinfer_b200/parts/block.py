@@ -47,8 +47,12 @@ class ParallelBlock:
         self.part_names = tuple(n for n in ("mixer_norm", "mixer", "ffn_norm", "ffn", "depth") if parts.get(n) is not None)
 
     def forward(self, x32: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
-        h_mixer = self.mixer_norm.forward(x32)
-        h_ffn = self.ffn_norm.forward(x32) if self.ffn is not None else None
+        together = getattr(self.mixer_norm, "forward_with", None) if type(self.mixer_norm) is type(self.ffn_norm) else None
+        if together is not None:        # two norms of one kind: the stream is read once
+            h_mixer, h_ffn = together(self.ffn_norm, x32)
+        else:
+            h_mixer = self.mixer_norm.forward(x32)
+            h_ffn = self.ffn_norm.forward(x32) if self.ffn is not None else None
         if self.depth is not None:
             self.depth.begin(x32, ctx)
         self.mixer.forward(h_mixer, x32, ctx, cache)

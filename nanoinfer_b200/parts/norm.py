@@ -39,6 +39,16 @@ class RMSNorm(Norm):
     def fold_into_projection(self, x32: torch.Tensor) -> Optional[FoldedNorm]:
         return FoldedNorm(x32, self.gain, self.eps, "rms")
 
+    def forward_with(self, other: "RMSNorm", x32: torch.Tensor):
+        """``(self.forward(x32), other.forward(x32))`` with the rows read once: for blocks whose branches read the same
+        stream through norms of their own. ``other`` must be an RMSNorm of the same size and eps."""
+        if other.size != self.size or other.eps != self.eps:
+            return self.forward(x32), other.forward(x32)
+        a = torch.empty((x32.shape[0], self.size), dtype=self.rt.dtype, device=x32.device)
+        b = torch.empty_like(a)
+        self.ops.rmsnorm_pair(x32, self.gain, other.gain, self.eps, a, b)
+        return a, b
+
 
 register_part("rmsnorm", RMSNorm)
 

@@ -71,6 +71,28 @@ def test_poly_norm(ops, dtype, rows, width):
     assert_close(out, ref, dtype, "poly_norm")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,width", [(1, 64), (9, 1000), (5, 4096), (3, 90)])
+def test_two_norms_of_one_row(ops, dtype, rows, width):
+    x, ga, gb = rnd(rows, width, seed=1, scale=3.0), rnd(width, seed=2), rnd(width, seed=3)
+    a, b = torch.empty(rows, width, dtype=dtype, device=DEV), torch.empty(rows, width, dtype=dtype, device=DEV)
+    ops.rmsnorm_pair(x, ga, gb, 1e-5, a, b)
+    base = x.double() / torch.sqrt(x.double().pow(2).mean(-1, keepdim=True) + 1e-5)
+    assert_close(a, base * ga.double(), dtype, "first norm")
+    assert_close(b, base * gb.double(), dtype, "second norm")
+
+
+@pytest.mark.parametrize("shape", [(7, 33), (16, 64)])
+def test_depth_mix_other_shapes(ops, shape):
+    hist, x = rnd(3, *shape, seed=2), rnd(*shape, seed=3)
+    coef = torch.tensor([0.5, -0.25, 1.5], device=DEV)
+    h_ref, x_ref = hist.cpu().clone(), x.cpu().clone()
+    TorchOps().depth_mix(h_ref, x_ref, coef.cpu(), 3)
+    ops.depth_mix(hist, x, coef, 3)
+    assert_close(x, x_ref, torch.float32, "depth_mix")
+    assert_close(hist, h_ref, torch.float32, "depth_mix history")
+
+
 def test_depth_mix_keeps_streams_and_sums_them(ops):
     hist = rnd(5, 7, 33, seed=2)
     x = rnd(7, 33, seed=3)

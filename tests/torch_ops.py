@@ -95,6 +95,10 @@ class TorchOps:
         out.copy_(res.view(m, -1).to(out.dtype))
 
     # ---- row-wise and element-wise kernels of pointwise.cu ------------------------------------------
+    def rmsnorm_pair(self, x32, gain_a32, gain_b32, eps, out_a, out_b):
+        self.rmsnorm(x32, gain_a32, eps, out_a)
+        self.rmsnorm(x32, gain_b32, eps, out_b)
+
     def poly_norm(self, z32, coef32, eps, out):
         z = z32.double()
         n = lambda y: y / torch.sqrt(y.pow(2).mean(-1, keepdim=True) + eps)
