@@ -146,6 +146,8 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 block_diag_smallm_kernel(const T* __restrict__ a, const T* __restrict__ w, const float* __restrict__ bias, float* __restrict__ out,
                          int blocks, int tokens, int n, int k) {
+    pdl_launch_dependents();
+    pdl_wait();      // the activations come from the kernel before
     const long long wid = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (wid >= (long long)blocks * n) return;
@@ -167,9 +169,9 @@ NIB_API int nib_block_diag_smallm(const void* a, const void* w, const float* bia
     if (tokens == 0) return 0;
     const int grid = ceil_div((long long)blocks * n, 4);
     if (dtype == NIB_F32)
-        block_diag_smallm_kernel<float><<<grid, 128, 0, stream>>>((const float*)a, (const float*)w, bias, out, blocks, tokens, n, k);
+        NIB_CUDA(launch_pdl(block_diag_smallm_kernel<float>, dim3(grid), dim3(128), (size_t)0, stream, (const float*)a, (const float*)w, bias, out, blocks, tokens, n, k));
     else if (dtype == NIB_BF16)
-        block_diag_smallm_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, bias, out, blocks, tokens, n, k);
+        NIB_CUDA(launch_pdl(block_diag_smallm_kernel<__nv_bfloat16>, dim3(grid), dim3(128), (size_t)0, stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, bias, out, blocks, tokens, n, k));
     else
         NIB_REQUIRE(false, "block-diagonal product: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();

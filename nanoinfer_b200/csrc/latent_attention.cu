@@ -26,6 +26,8 @@ latent_store_kernel(const float* __restrict__ z, int ldz, const float* __restric
                     const float* __restrict__ freq, float mag, const int* __restrict__ positions,
                     const int* __restrict__ req_index, const int* __restrict__ block_table, int bt_stride, int page_size,
                     T* __restrict__ pages, int num_pages, int tokens, int rank, int rot) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     const int t = blockIdx.x * LAT_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= tokens) return;
     const int pos = positions[t];
@@ -55,11 +57,11 @@ NIB_API int nib_latent_store(const float* z, int ldz, const float* gain, float e
     if (tokens == 0) return 0;
     const int grid = ceil_div(tokens, LAT_WARPS);
     if (dtype == NIB_F32)
-        latent_store_kernel<float><<<grid, LAT_WARPS * 32, 0, stream>>>(z, ldz, gain, eps, freq, mag, positions, req_index,
-            block_table, bt_stride, page_size, (float*)pages, num_pages, tokens, rank, rot);
+        NIB_CUDA(launch_pdl(latent_store_kernel<float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, z, ldz, gain, eps, freq, mag, positions, req_index,
+            block_table, bt_stride, page_size, (float*)pages, num_pages, tokens, rank, rot));
     else if (dtype == NIB_BF16)
-        latent_store_kernel<__nv_bfloat16><<<grid, LAT_WARPS * 32, 0, stream>>>(z, ldz, gain, eps, freq, mag, positions, req_index,
-            block_table, bt_stride, page_size, (__nv_bfloat16*)pages, num_pages, tokens, rank, rot);
+        NIB_CUDA(launch_pdl(latent_store_kernel<__nv_bfloat16>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, z, ldz, gain, eps, freq, mag, positions, req_index,
+            block_table, bt_stride, page_size, (__nv_bfloat16*)pages, num_pages, tokens, rank, rot));
     else
         NIB_REQUIRE(false, "latent_store: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();
@@ -75,6 +77,8 @@ template <typename T, typename TQ>
 __global__ void __launch_bounds__(LAT_WARPS * 32)
 latent_query_kernel(const float* __restrict__ q, int ldq_in, const T* __restrict__ w_uk, const float* __restrict__ freq, float mag,
                     const int* __restrict__ positions, TQ* __restrict__ qa, int ldq, int tokens, int heads, int dn, int rank, int rot) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     const long long w = (long long)blockIdx.x * LAT_WARPS + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (w >= (long long)tokens * heads) return;
@@ -117,11 +121,11 @@ NIB_API int nib_latent_query(const float* q, int ldq_in, const void* w_uk, const
     if (tokens == 0) return 0;
     const int grid = ceil_div((long long)tokens * heads, LAT_WARPS);
     if (dtype == NIB_F32 && q_dtype == NIB_F32)
-        latent_query_kernel<float, float><<<grid, LAT_WARPS * 32, 0, stream>>>(q, ldq_in, (const float*)w_uk, freq, mag, positions, (float*)qa, ldq, tokens, heads, dn, rank, rot);
+        NIB_CUDA(launch_pdl(latent_query_kernel<float, float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, q, ldq_in, (const float*)w_uk, freq, mag, positions, (float*)qa, ldq, tokens, heads, dn, rank, rot));
     else if (dtype == NIB_BF16 && q_dtype == NIB_F32)
-        latent_query_kernel<__nv_bfloat16, float><<<grid, LAT_WARPS * 32, 0, stream>>>(q, ldq_in, (const __nv_bfloat16*)w_uk, freq, mag, positions, (float*)qa, ldq, tokens, heads, dn, rank, rot);
+        NIB_CUDA(launch_pdl(latent_query_kernel<__nv_bfloat16, float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, q, ldq_in, (const __nv_bfloat16*)w_uk, freq, mag, positions, (float*)qa, ldq, tokens, heads, dn, rank, rot));
     else if (dtype == NIB_BF16 && q_dtype == NIB_BF16)
-        latent_query_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, LAT_WARPS * 32, 0, stream>>>(q, ldq_in, (const __nv_bfloat16*)w_uk, freq, mag, positions, (__nv_bfloat16*)qa, ldq, tokens, heads, dn, rank, rot);
+        NIB_CUDA(launch_pdl(latent_query_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, q, ldq_in, (const __nv_bfloat16*)w_uk, freq, mag, positions, (__nv_bfloat16*)qa, ldq, tokens, heads, dn, rank, rot));
     else
         NIB_REQUIRE(false, "latent_query: unsupported types %d / %d", dtype, q_dtype);
     NIB_LAUNCH_CHECK();
@@ -137,6 +141,8 @@ __global__ void __launch_bounds__(LAT_WARPS * 32)
 latent_attention_kernel(const float* __restrict__ qa, float* __restrict__ out, const int* __restrict__ positions,
                         const int* __restrict__ req_index, const int* __restrict__ block_table, int bt_stride, int page_size,
                         const T* __restrict__ pages, int num_pages, int tokens, int heads, int rank, int rot, float scale, int window) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     __shared__ float q_s[LAT_WARPS][LAT_MAX_ROW];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long w = (long long)blockIdx.x * LAT_WARPS + warp;
@@ -206,11 +212,11 @@ NIB_API int nib_latent_attention(const float* qa, float* out, const int* positio
     if (tokens == 0) return 0;
     const int grid = ceil_div((long long)tokens * heads, LAT_WARPS);
     if (dtype == NIB_F32)
-        latent_attention_kernel<float><<<grid, LAT_WARPS * 32, 0, stream>>>(qa, out, positions, req_index, block_table, bt_stride,
-            page_size, (const float*)pages, num_pages, tokens, heads, rank, rot, scale, window);
+        NIB_CUDA(launch_pdl(latent_attention_kernel<float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, qa, out, positions, req_index, block_table, bt_stride,
+            page_size, (const float*)pages, num_pages, tokens, heads, rank, rot, scale, window));
     else if (dtype == NIB_BF16)
-        latent_attention_kernel<__nv_bfloat16><<<grid, LAT_WARPS * 32, 0, stream>>>(qa, out, positions, req_index, block_table, bt_stride,
-            page_size, (const __nv_bfloat16*)pages, num_pages, tokens, heads, rank, rot, scale, window);
+        NIB_CUDA(launch_pdl(latent_attention_kernel<__nv_bfloat16>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, qa, out, positions, req_index, block_table, bt_stride,
+            page_size, (const __nv_bfloat16*)pages, num_pages, tokens, heads, rank, rot, scale, window));
     else
         NIB_REQUIRE(false, "latent attention: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();
@@ -224,6 +230,8 @@ template <typename T>
 __global__ void __launch_bounds__(LAT_WARPS * 32)
 latent_value_kernel(const float* __restrict__ lat, const T* __restrict__ w_uv, T* __restrict__ out, int ldo, int tokens,
                     int heads, int dv, int rank) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     __shared__ float l_s[LAT_WARPS][LAT_MAX_RANK];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long w = (long long)blockIdx.x * LAT_WARPS + warp;
@@ -246,9 +254,9 @@ NIB_API int nib_latent_value(const float* lat, const void* w_uv, void* out, int 
     if (tokens == 0) return 0;
     const int grid = ceil_div((long long)tokens * heads, LAT_WARPS);
     if (dtype == NIB_F32)
-        latent_value_kernel<float><<<grid, LAT_WARPS * 32, 0, stream>>>(lat, (const float*)w_uv, (float*)out, ldo, tokens, heads, dv, rank);
+        NIB_CUDA(launch_pdl(latent_value_kernel<float>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, lat, (const float*)w_uv, (float*)out, ldo, tokens, heads, dv, rank));
     else if (dtype == NIB_BF16)
-        latent_value_kernel<__nv_bfloat16><<<grid, LAT_WARPS * 32, 0, stream>>>(lat, (const __nv_bfloat16*)w_uv, (__nv_bfloat16*)out, ldo, tokens, heads, dv, rank);
+        NIB_CUDA(launch_pdl(latent_value_kernel<__nv_bfloat16>, dim3(grid), dim3(LAT_WARPS * 32), (size_t)(0), stream, lat, (const __nv_bfloat16*)w_uv, (__nv_bfloat16*)out, ldo, tokens, heads, dv, rank));
     else
         NIB_REQUIRE(false, "latent_value: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();

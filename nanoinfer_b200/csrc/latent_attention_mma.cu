@@ -94,6 +94,8 @@ __global__ void __launch_bounds__(LM_WARPS * 32)
 latent_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restrict__ out, const int* __restrict__ q_start,
                           const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride, int page_size,
                           const __nv_bfloat16* __restrict__ pages, int num_pages, int heads, int rank, int width, float scale, int window) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     extern __shared__ __align__(16) unsigned char smem[];
     const int req = blockIdx.y;
     const int row_begin = q_start[req], q_len = q_start[req + 1] - row_begin;
@@ -177,6 +179,8 @@ latent_decode_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restrict
                          const int* __restrict__ block_table, int bt_stride, int page_size, const __nv_bfloat16* __restrict__ pages,
                          int num_pages, int heads, int rank, int width, float scale, int window, int splits,
                          float* __restrict__ part_o, float* __restrict__ part_ml) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     extern __shared__ __align__(16) unsigned char smem[];
     const int split = blockIdx.x, token = blockIdx.y, h0 = blockIdx.z * 16;
     const int n_rows = min(16, heads - h0);
@@ -270,6 +274,8 @@ latent_decode_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restrict
 __global__ void __launch_bounds__(128)
 latent_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, float* __restrict__ out,
                              int rows, int splits, int dvp, int rank) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (w >= rows) return;
     float m = -INFINITY;
@@ -298,8 +304,8 @@ int lm_launch(bool decode, const __nv_bfloat16* qa, float* out, const int* q_sta
         const size_t smem = 2 * (size_t)LTile<DKP>::BYTES;
         NIB_CUDA(cudaFuncSetAttribute(latent_prefill_mma_kernel<DKP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         const dim3 grid(ceil_div((long long)max_q_len * heads, LM_WARPS * 16), requests);
-        latent_prefill_mma_kernel<DKP, DVP><<<grid, LM_WARPS * 32, smem, stream>>>(qa, out, q_start, ctx_lens, bt, bt_stride, page_size,
-                                                                                   pages, num_pages, heads, rank, width, scale, window);
+        NIB_CUDA(launch_pdl(latent_prefill_mma_kernel<DKP, DVP>, dim3(grid), dim3(LM_WARPS * 32), (size_t)(smem), stream, qa, out, q_start, ctx_lens, bt, bt_stride, page_size,
+                                                                                   pages, num_pages, heads, rank, width, scale, window));
         NIB_LAUNCH_CHECK();
         return 0;
     }
@@ -308,12 +314,12 @@ int lm_launch(bool decode, const __nv_bfloat16* qa, float* out, const int* q_sta
     if (merge > smem) smem = merge;
     NIB_CUDA(cudaFuncSetAttribute(latent_decode_mma_kernel<DKP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const dim3 grid(splits, requests, ceil_div(heads, 16));
-    latent_decode_mma_kernel<DKP, DVP><<<grid, LM_WARPS * 32, smem, stream>>>(qa, out, ctx_lens, bt, bt_stride, page_size, pages, num_pages,
-                                                                              heads, rank, width, scale, window, splits, part_o, part_ml);
+    NIB_CUDA(launch_pdl(latent_decode_mma_kernel<DKP, DVP>, dim3(grid), dim3(LM_WARPS * 32), (size_t)(smem), stream, qa, out, ctx_lens, bt, bt_stride, page_size, pages, num_pages,
+                                                                              heads, rank, width, scale, window, splits, part_o, part_ml));
     NIB_LAUNCH_CHECK();
     if (splits > 1) {
         const int rows = requests * heads;
-        latent_decode_combine_kernel<<<ceil_div(rows, 4), 128, 0, stream>>>(part_o, part_ml, out, rows, splits, DVP, rank);
+        NIB_CUDA(launch_pdl(latent_decode_combine_kernel, dim3(ceil_div(rows, 4)), dim3(128), (size_t)(0), stream, part_o, part_ml, out, rows, splits, DVP, rank));
         NIB_LAUNCH_CHECK();
     }
     return 0;

@@ -23,6 +23,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 poly_norm_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ coef, T* __restrict__ out, int ldo,
                  int width, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     __shared__ float part[8];
     const float* zr = z + (size_t)blockIdx.x * ldz;
     float s2 = 0.f, s4 = 0.f, s6 = 0.f;
@@ -49,8 +51,8 @@ NIB_API int nib_poly_norm(const float* z, int ldz, const float* coef, void* out,
                           int dtype, cudaStream_t stream) {
     NIB_REQUIRE(rows >= 0 && width > 0 && ldz >= width && ldo >= width, "poly_norm: bad sizes rows=%d width=%d", rows, width);
     if (rows == 0) return 0;
-    if (dtype == NIB_F32) poly_norm_kernel<float><<<rows, 256, 0, stream>>>(z, ldz, coef, (float*)out, ldo, width, eps);
-    else if (dtype == NIB_BF16) poly_norm_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>(z, ldz, coef, (__nv_bfloat16*)out, ldo, width, eps);
+    if (dtype == NIB_F32) NIB_CUDA(launch_pdl(poly_norm_kernel<float>, dim3(rows), dim3(256), (size_t)(0), stream, z, ldz, coef, (float*)out, ldo, width, eps));
+    else if (dtype == NIB_BF16) NIB_CUDA(launch_pdl(poly_norm_kernel<__nv_bfloat16>, dim3(rows), dim3(256), (size_t)(0), stream, z, ldz, coef, (__nv_bfloat16*)out, ldo, width, eps));
     else NIB_REQUIRE(false, "poly_norm: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();
     return 0;
@@ -61,6 +63,8 @@ NIB_API int nib_poly_norm(const float* z, int ldz, const float* coef, void* out,
 // becomes sum_{j < n} coef[j] * hist[j], added in ascending j.
 __global__ void depth_mix_kernel(float* __restrict__ hist, float* __restrict__ x, const float* __restrict__ coef, int n,
                                  long long n_elem) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_elem) return;
     const float newest = x[i];
@@ -73,6 +77,8 @@ __global__ void depth_mix_kernel(float* __restrict__ hist, float* __restrict__ x
 // the same with four elements a thread (n_elem a multiple of 4, 16-byte aligned streams)
 __global__ void depth_mix4_kernel(float4* __restrict__ hist, float4* __restrict__ x, const float* __restrict__ coef, int n,
                                   long long n_vec) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_vec) return;
     const float4 newest = x[i];
@@ -91,9 +97,9 @@ NIB_API int nib_depth_mix(float* hist, float* x, const float* coef, int n, long 
     NIB_REQUIRE(n >= 1 && n_elem >= 0, "depth_mix: bad sizes n=%d", n);
     if (n_elem == 0) return 0;
     if (n_elem % 4 == 0 && (((uintptr_t)hist | (uintptr_t)x) & 15) == 0)
-        depth_mix4_kernel<<<ceil_div(n_elem / 4, 256), 256, 0, stream>>>((float4*)hist, (float4*)x, coef, n, n_elem / 4);
+        NIB_CUDA(launch_pdl(depth_mix4_kernel, dim3(ceil_div(n_elem / 4, 256)), dim3(256), (size_t)(0), stream, (float4*)hist, (float4*)x, coef, n, n_elem / 4));
     else
-        depth_mix_kernel<<<ceil_div(n_elem, 256), 256, 0, stream>>>(hist, x, coef, n, n_elem);
+        NIB_CUDA(launch_pdl(depth_mix_kernel, dim3(ceil_div(n_elem, 256)), dim3(256), (size_t)(0), stream, hist, x, coef, n, n_elem));
     NIB_LAUNCH_CHECK();
     return 0;
 }
@@ -102,6 +108,8 @@ NIB_API int nib_depth_mix(float* hist, float* x, const float* coef, int n, long 
 // out[t, c] = f(in[t, c]) for c < width; kind 0: tanh, 1: identity, 2: sigmoid.
 template <typename T>
 __global__ void unary_kernel(const float* __restrict__ in, int ld_in, T* __restrict__ out, int ld_out, int rows, int width, int kind) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)rows * width) return;
     const int t = (int)(i / width), c = (int)(i % width);
@@ -116,8 +124,8 @@ NIB_API int nib_unary(const float* in, int ld_in, void* out, int ld_out, int row
     NIB_REQUIRE(rows >= 0 && width > 0 && kind >= 0 && kind <= 2, "unary: bad arguments");
     if (rows == 0) return 0;
     const int blocks = ceil_div((long long)rows * width, 256);
-    if (dtype == NIB_F32) unary_kernel<float><<<blocks, 256, 0, stream>>>(in, ld_in, (float*)out, ld_out, rows, width, kind);
-    else if (dtype == NIB_BF16) unary_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(in, ld_in, (__nv_bfloat16*)out, ld_out, rows, width, kind);
+    if (dtype == NIB_F32) NIB_CUDA(launch_pdl(unary_kernel<float>, dim3(blocks), dim3(256), (size_t)(0), stream, in, ld_in, (float*)out, ld_out, rows, width, kind));
+    else if (dtype == NIB_BF16) NIB_CUDA(launch_pdl(unary_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), (size_t)(0), stream, in, ld_in, (__nv_bfloat16*)out, ld_out, rows, width, kind));
     else NIB_REQUIRE(false, "unary: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();
     return 0;
@@ -130,6 +138,8 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ gate, int ldg,
                       const float* __restrict__ gain, T* __restrict__ out, int ld_out, int tokens, int heads, int d, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (w >= (long long)tokens * heads) return;
@@ -151,8 +161,8 @@ NIB_API int nib_head_norm_gate(const float* o, int ldo, const float* gate, int l
     NIB_REQUIRE(tokens >= 0 && heads > 0 && d > 0, "head_norm_gate: bad sizes");
     if (tokens == 0) return 0;
     const int blocks = ceil_div((long long)tokens * heads, 4);
-    if (dtype == NIB_F32) head_norm_gate_kernel<float><<<blocks, 128, 0, stream>>>(o, ldo, gate, ldg, gain, (float*)out, ld_out, tokens, heads, d, eps);
-    else if (dtype == NIB_BF16) head_norm_gate_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(o, ldo, gate, ldg, gain, (__nv_bfloat16*)out, ld_out, tokens, heads, d, eps);
+    if (dtype == NIB_F32) NIB_CUDA(launch_pdl(head_norm_gate_kernel<float>, dim3(blocks), dim3(128), (size_t)(0), stream, o, ldo, gate, ldg, gain, (float*)out, ld_out, tokens, heads, d, eps));
+    else if (dtype == NIB_BF16) NIB_CUDA(launch_pdl(head_norm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), (size_t)(0), stream, o, ldo, gate, ldg, gain, (__nv_bfloat16*)out, ld_out, tokens, heads, d, eps));
     else NIB_REQUIRE(false, "head_norm_gate: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();
     return 0;
@@ -166,6 +176,8 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(256)
 rmsnorm_pair_kernel(const float* __restrict__ x, const float* __restrict__ gain_a, const float* __restrict__ gain_b,
                     T* __restrict__ out_a, T* __restrict__ out_b, int n_rows, int hidden, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= n_rows) return;
@@ -209,7 +221,7 @@ NIB_API int nib_rmsnorm_pair(const float* x, const float* gain_a, const float* g
     if (n_rows == 0) return 0;
     const int warps = n_rows >= 8 ? 8 : n_rows;
     const dim3 grid(ceil_div(n_rows, warps)), block(32 * warps);
-#define NIB_RP(T, NV) rmsnorm_pair_kernel<T, NV><<<grid, block, 0, stream>>>(x, gain_a, gain_b, (T*)out_a, (T*)out_b, n_rows, hidden, eps)
+#define NIB_RP(T, NV) NIB_CUDA(launch_pdl(rmsnorm_pair_kernel<T, NV>, dim3(grid), dim3(block), (size_t)(0), stream, x, gain_a, gain_b, (T*)out_a, (T*)out_b, n_rows, hidden, eps))
     if (dtype == NIB_F32) {
         if (hidden <= 1024) NIB_RP(float, 8); else if (hidden <= 2048) NIB_RP(float, 16); else NIB_RP(float, 32);
     } else {

@@ -30,6 +30,8 @@ constexpr int DR_THREADS = DR_CV * DR_LPC;
 __global__ void __launch_bounds__(128)
 delta_rule_prepare_kernel(const float* __restrict__ k, const float* __restrict__ a_logit, int ld, const float* __restrict__ w_logit,
                           int ldw, float* __restrict__ work, int tokens, int heads, int d) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     const long long wid = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (wid >= (long long)tokens * heads) return;
@@ -53,6 +55,8 @@ __global__ void __launch_bounds__(DR_THREADS)
 delta_rule_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v, int ld,
                        const float* __restrict__ work, float* __restrict__ state, const int* __restrict__ q_start,
                        const int* __restrict__ slots, float* __restrict__ o, int ldo, int tokens, int heads, int d) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     constexpr bool VEC = KR % 4 == 0;
     // a lane's slice, padded to an odd number of 16-byte units so that the eight lanes' 16-byte loads fall into distinct banks
     constexpr int KRP = (VEC && (KR / 4) % 2 == 0) ? KR + 4 : KR;
@@ -189,14 +193,14 @@ NIB_API int nib_delta_rule_scan(const float* r, const float* k, const float* v, 
                                 float* o, int ldo, float* work, int tokens, int requests, int heads, int d, cudaStream_t stream) {
     NIB_REQUIRE(requests >= 0 && heads > 0 && d > 0 && d <= 256, "delta_rule_scan: head size %d is outside 1..256", d);
     if (requests == 0 || tokens == 0) return 0;
-    delta_rule_prepare_kernel<<<ceil_div((long long)tokens * heads, 4), 128, 0, stream>>>(k, a_logit, ld, w_logit, ldw, work, tokens, heads, d);
+    NIB_CUDA(launch_pdl(delta_rule_prepare_kernel, dim3(ceil_div((long long)tokens * heads, 4)), dim3(128), (size_t)(0), stream, k, a_logit, ld, w_logit, ldw, work, tokens, heads, d));
     NIB_LAUNCH_CHECK();
     const dim3 grid(ceil_div(d, DR_CV), heads, requests);
     const int kr = ceil_div(d, DR_LPC);
 #define NIB_DR(KR)                                                                                                         \
     if (kr <= KR) {                                                                                                        \
-        delta_rule_scan_kernel<KR><<<grid, DR_THREADS, 0, stream>>>(r, k, v, ld, work, state, q_start, slots, o, ldo, tokens, \
-                                                                    heads, d);                                             \
+        NIB_CUDA(launch_pdl(delta_rule_scan_kernel<KR>, dim3(grid), dim3(DR_THREADS), (size_t)(0), stream, r, k, v, ld, work, state, q_start, slots, o, ldo, tokens, \
+                                                                    heads, d));                                             \
         NIB_LAUNCH_CHECK();                                                                                                \
         return 0;                                                                                                          \
     }
@@ -217,6 +221,8 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, int ldx, const f
                                    const float* __restrict__ state, int rows_per_slot, int hist_row0,
                                    const int* __restrict__ q_start, const int* __restrict__ req_index, const int* __restrict__ slots,
                                    float* __restrict__ u32, T* __restrict__ u_blocks, int tokens, int width, int taps, int blocks) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)tokens * width) return;
     const int t = (int)(i / width), c = (int)(i % width);
@@ -241,11 +247,11 @@ NIB_API int nib_causal_conv(const float* x, int ldx, const float* w, const float
     if (tokens == 0) return 0;
     const int grid = ceil_div((long long)tokens * width, 256);
     if (dtype == NIB_F32)
-        causal_conv_kernel<float><<<grid, 256, 0, stream>>>(x, ldx, w, bias, state, rows_per_slot, hist_row0, q_start, req_index,
-                                                            slots, u32, (float*)u_blocks, tokens, width, taps, blocks);
+        NIB_CUDA(launch_pdl(causal_conv_kernel<float>, dim3(grid), dim3(256), (size_t)(0), stream, x, ldx, w, bias, state, rows_per_slot, hist_row0, q_start, req_index,
+                                                            slots, u32, (float*)u_blocks, tokens, width, taps, blocks));
     else if (dtype == NIB_BF16)
-        causal_conv_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(x, ldx, w, bias, state, rows_per_slot, hist_row0, q_start,
-                                                                    req_index, slots, u32, (__nv_bfloat16*)u_blocks, tokens, width, taps, blocks);
+        NIB_CUDA(launch_pdl(causal_conv_kernel<__nv_bfloat16>, dim3(grid), dim3(256), (size_t)(0), stream, x, ldx, w, bias, state, rows_per_slot, hist_row0, q_start,
+                                                                    req_index, slots, u32, (__nv_bfloat16*)u_blocks, tokens, width, taps, blocks));
     else
         NIB_REQUIRE(false, "causal_conv: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();
@@ -269,6 +275,8 @@ constexpr int LRU_AHEAD = 8;
 __global__ void rglru_gate_kernel(const float* __restrict__ u32, const float* __restrict__ gates, const float* __restrict__ y_logit,
                                   int ldy, const float* __restrict__ softplus_lam, float* __restrict__ work, int tokens, int width,
                                   int blocks) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long n = (long long)tokens * width;
     if (i >= n) return;
@@ -287,6 +295,8 @@ template <typename T>
 __global__ void __launch_bounds__(LRU_WARPS * 32)
 rglru_scan_kernel(const float* __restrict__ work, const float* __restrict__ x, int ldx, float* __restrict__ state,
                   const int* __restrict__ q_start, const int* __restrict__ slots, T* __restrict__ out, int tokens, int width, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
     __shared__ float s_a[LRU_WARPS][32], s_b[LRU_WARPS][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + lane;
@@ -355,15 +365,15 @@ NIB_API int nib_rglru_scan(const float* u32, const float* gates, const float* y_
                 "rglru_scan: bad sizes (width %d, taps %d of at most %d, blocks %d)", width, taps, LRU_MAX_TAPS, blocks);
     NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "rglru_scan: unknown dtype %d", dtype);
     if (requests == 0 || tokens == 0) return 0;
-    rglru_gate_kernel<<<ceil_div((long long)tokens * width, 256), 256, 0, stream>>>(u32, gates, y_logit, ldy, softplus_lam, work,
-                                                                                    tokens, width, blocks);
+    NIB_CUDA(launch_pdl(rglru_gate_kernel, dim3(ceil_div((long long)tokens * width, 256)), dim3(256), (size_t)(0), stream, u32, gates, y_logit, ldy, softplus_lam, work,
+                                                                                    tokens, width, blocks));
     NIB_LAUNCH_CHECK();
     const dim3 grid(ceil_div(width, 32), requests);
     if (dtype == NIB_F32)
-        rglru_scan_kernel<float><<<grid, LRU_WARPS * 32, 0, stream>>>(work, x, ldx, state, q_start, slots, (float*)out, tokens, width, taps);
+        NIB_CUDA(launch_pdl(rglru_scan_kernel<float>, dim3(grid), dim3(LRU_WARPS * 32), (size_t)(0), stream, work, x, ldx, state, q_start, slots, (float*)out, tokens, width, taps));
     else
-        rglru_scan_kernel<__nv_bfloat16><<<grid, LRU_WARPS * 32, 0, stream>>>(work, x, ldx, state, q_start, slots, (__nv_bfloat16*)out,
-                                                                              tokens, width, taps);
+        NIB_CUDA(launch_pdl(rglru_scan_kernel<__nv_bfloat16>, dim3(grid), dim3(LRU_WARPS * 32), (size_t)(0), stream, work, x, ldx, state, q_start, slots, (__nv_bfloat16*)out,
+                                                                              tokens, width, taps));
     NIB_LAUNCH_CHECK();
     return 0;
 }
