@@ -94,8 +94,7 @@ __global__ void __launch_bounds__(LM_WARPS * 32)
 latent_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restrict__ out, const int* __restrict__ q_start,
                           const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride, int page_size,
                           const __nv_bfloat16* __restrict__ pages, int num_pages, int heads, int rank, int width, float scale, int window) {
-    pdl_launch_dependents();
-    pdl_wait();      // everything this kernel reads may come from the kernel before
+        pdl_wait();      // everything this kernel reads may come from the kernel before
     extern __shared__ __align__(16) unsigned char smem[];
     const int req = blockIdx.y;
     const int row_begin = q_start[req], q_len = q_start[req + 1] - row_begin;
@@ -157,6 +156,7 @@ latent_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restric
         __syncthreads();
     }
     lm_wait<0>();
+    pdl_launch_dependents();        // only now: the next kernel's blocks would take room from tiles still at work
     const int t = lane & 3;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -332,6 +332,141 @@ int lm_dvp(int rank, int dkp) {
     return dkp;
 }
 
+// ------------------------------------------------------------------------------------------ per-head products
+// The two maps between a head's own space and the latent space, for many tokens at once: one small matrix per head,
+// 16 tokens per warp, the head's matrix staged in shared memory 64 output columns at a time. A comes from 32-bit
+// activations, rounded to bfloat16 as it is put into fragments.
+__device__ __forceinline__ void lm_a_from_f32(unsigned (&a)[4], const float* const (&row)[2], int k0, int k, int lane) {
+    const int t = lane & 3;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (row[r]) {
+            const int c = k0 + 2 * t;
+            if (c < k) v[0] = row[r][c];
+            if (c + 1 < k) v[1] = row[r][c + 1];
+            if (c + 8 < k) v[2] = row[r][c + 8];
+            if (c + 9 < k) v[3] = row[r][c + 9];
+        }
+        a[r] = pack_bf16(v[0], v[1]);
+        a[2 + r] = pack_bf16(v[2], v[3]);
+    }
+}
+
+// out[t, h, n] = sum_k a[t, h, k] * w[h, n, k] (w: [heads, n, k] bfloat16, its rows are the output features).
+// grid: (token tiles of 64, heads). a: floats, `lda` elements per token, the head's k values at h * k.
+template <int KP>
+__global__ void __launch_bounds__(LM_WARPS * 32)
+head_product_nk_kernel(const float* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, int ldo,
+                       int tokens, int n, int k) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const float* row[2];
+    int tok[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        tok[r] = blockIdx.x * (LM_WARPS * 16) + warp * 16 + g + 8 * r;
+        row[r] = tok[r] < tokens ? a + (size_t)tok[r] * lda + (size_t)h * k : nullptr;
+    }
+    unsigned af[KP / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < KP / 16; ++kk) lm_a_from_f32(af[kk], row, kk * 16, k, lane);
+    const __nv_bfloat16* wh = w + (size_t)h * n * k;
+    for (int n0 = 0; n0 < n; n0 += LM_BLOCK_N) {
+        __syncthreads();
+        constexpr int CPR = LTile<KP>::CPR;
+        for (int i = tid; i < LM_BLOCK_N * CPR; i += LM_WARPS * 32) {
+            const int r = i / CPR, c = i - r * CPR;
+            const bool valid = n0 + r < n && c * 8 < k;
+            lm_cp_async_16(smem + r * LTile<KP>::ROW_BYTES + c * 16, wh + (valid ? (size_t)(n0 + r) * k + c * 8 : 0), valid);
+        }
+        lm_commit();
+        lm_wait<0>();
+        __syncthreads();
+        float s[LM_BLOCK_N / 8][4];
+#pragma unroll
+        for (int j = 0; j < LM_BLOCK_N / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+        lm_qk<KP, LM_BLOCK_N / 8>(s, af, smem, 0, lane);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            if (tok[r] >= tokens) continue;
+            __nv_bfloat16* o = out + (size_t)tok[r] * ldo + (size_t)h * n + n0;
+#pragma unroll
+            for (int j = 0; j < LM_BLOCK_N / 8; ++j)
+                if (n0 + j * 8 + 2 * t4 < n)
+                    *reinterpret_cast<unsigned*>(o + j * 8 + 2 * t4) = pack_bf16(s[j][2 * r], s[j][2 * r + 1]);
+        }
+    }
+}
+
+// qa[t, h, c] = sum_d q[t, h, d] * w[h, d, c] for c < n (w: [heads, k, n] bfloat16, its rows are the inputs), then the
+// rotated part: qa[t, h, n + 2i], [.. + 1] = the pair q[t, h, k + 2i], [.. + 1] turned by position * freq[i], and zeros up
+// to ldq. grid: (token tiles of 64, heads). q: floats, `ldq_in` elements per token, a head's k + rot values together.
+template <int KP>
+__global__ void __launch_bounds__(LM_WARPS * 32)
+head_product_kn_kernel(const float* __restrict__ q, int ldq_in, const __nv_bfloat16* __restrict__ w, const float* __restrict__ freq,
+                       float mag, const int* __restrict__ positions, __nv_bfloat16* __restrict__ qa, int ldq, int tokens, int heads,
+                       int n, int k, int rot) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const float* row[2];
+    int tok[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        tok[r] = blockIdx.x * (LM_WARPS * 16) + warp * 16 + g + 8 * r;
+        row[r] = tok[r] < tokens ? q + (size_t)tok[r] * ldq_in + (size_t)h * (k + rot) : nullptr;
+    }
+    unsigned af[KP / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < KP / 16; ++kk) lm_a_from_f32(af[kk], row, kk * 16, k, lane);
+    const __nv_bfloat16* wh = w + (size_t)h * k * n;
+    for (int n0 = 0; n0 < n; n0 += LM_BLOCK_N) {
+        __syncthreads();
+        constexpr int CPR = LM_BLOCK_N / 8;         // a tile row holds 64 output columns of one input d
+        for (int i = tid; i < KP * CPR; i += LM_WARPS * 32) {
+            const int d = i / CPR, c = i - d * CPR;
+            const bool valid = d < k && n0 + c * 8 < n;
+            lm_cp_async_16(smem + d * LTile<LM_BLOCK_N>::ROW_BYTES + c * 16, wh + (valid ? (size_t)d * n + n0 + c * 8 : 0), valid);
+        }
+        lm_commit();
+        lm_wait<0>();
+        __syncthreads();
+        float o[LM_BLOCK_N / 8][4];
+#pragma unroll
+        for (int j = 0; j < LM_BLOCK_N / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+        lm_pv<LM_BLOCK_N, LM_BLOCK_N, KP / 16>(o, af, smem, 0, lane);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            if (tok[r] >= tokens) continue;
+            __nv_bfloat16* dst = qa + ((size_t)tok[r] * heads + h) * ldq + n0;
+#pragma unroll
+            for (int j = 0; j < LM_BLOCK_N / 8; ++j)
+                if (n0 + j * 8 + 2 * t4 < n)
+                    *reinterpret_cast<unsigned*>(dst + j * 8 + 2 * t4) = pack_bf16(o[j][2 * r], o[j][2 * r + 1]);
+        }
+    }
+    // the rotated part and the padding of the warp's 16 rows
+    for (int rr = 0; rr < 16; ++rr) {
+        const int token = blockIdx.x * (LM_WARPS * 16) + warp * 16 + rr;
+        if (token >= tokens) break;
+        const float* qr = q + (size_t)token * ldq_in + (size_t)h * (k + rot) + k;
+        __nv_bfloat16* dst = qa + ((size_t)token * heads + h) * ldq + n;
+        const float pos = (float)positions[token];
+        for (int i = lane; i < rot / 2; i += 32) {
+            const float ang = pos * freq[i];
+            const float cs = cosf(ang) * mag, sn = sinf(ang) * mag;
+            const float x = qr[2 * i], y = qr[2 * i + 1];
+            dst[2 * i] = __float2bfloat16_rn(x * cs - y * sn);
+            dst[2 * i + 1] = __float2bfloat16_rn(y * cs + x * sn);
+        }
+        for (int c = n + rot + lane; c < ldq; c += 32) qa[((size_t)token * heads + h) * ldq + c] = __float2bfloat16_rn(0.f);
+    }
+}
+
 }  // namespace
 
 // 1 if the tensor-core kernels take this shape: rows of up to 192 elements whose byte size is a multiple of 16.
@@ -365,5 +500,51 @@ NIB_API int nib_latent_attention_mma(int decode, const void* qa, void* out, cons
     NIB_LM(144, 32) NIB_LM(160, 32) NIB_LM(176, 32) NIB_LM(192, 32) NIB_LM(144, 144) NIB_LM(160, 160) NIB_LM(176, 176) NIB_LM(192, 192)
 #undef NIB_LM
     NIB_REQUIRE(false, "latent attention (tensor cores): no kernel for a row of %d and a latent of %d", dkp, dvp);
+    return 0;
+}
+
+// 1 if the per-head products on the tensor cores take these sizes (k: the contraction, n: the output columns).
+NIB_API int nib_head_product_supported(int kn_layout, int k, int n) {
+    if (kn_layout) return (k >= 1 && k <= 128 && n % 8 == 0 && n >= 8) ? 1 : 0;
+    return (k % 8 == 0 && k >= 8 && k <= 192 && n % 2 == 0 && n >= 2) ? 1 : 0;
+}
+
+// out[t, h, :n] = a[t, h, :k] . w[h]^T, w: [heads, n, k] (values out of the latent space: k = latent, n = value width).
+NIB_API int nib_head_product_nk(const float* a, int lda, const void* w, void* out, int ldo, int tokens, int heads, int n, int k,
+                                cudaStream_t stream) {
+    NIB_REQUIRE(nib_head_product_supported(0, k, n) == 1 && tokens >= 0 && heads > 0, "per-head product: sizes k=%d n=%d are not supported", k, n);
+    if (tokens == 0) return 0;
+    const dim3 grid(ceil_div(tokens, LM_WARPS * 16), heads);
+    const int kp = (k + 15) / 16 * 16;
+#define NIB_HP(KP)                                                                                                                  \
+    if (kp == KP) {                                                                                                                 \
+        NIB_CUDA(launch_pdl(head_product_nk_kernel<KP>, grid, dim3(LM_WARPS * 32), (size_t)LTile<KP>::BYTES, stream, a, lda,       \
+                            (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, tokens, n, k));                                     \
+        return 0;                                                                                                                   \
+    }
+    NIB_HP(16) NIB_HP(32) NIB_HP(48) NIB_HP(64) NIB_HP(80) NIB_HP(96) NIB_HP(112) NIB_HP(128) NIB_HP(144) NIB_HP(160) NIB_HP(176) NIB_HP(192)
+#undef NIB_HP
+    NIB_REQUIRE(false, "per-head product: k=%d", k);
+    return 0;
+}
+
+// qa[t, h] = [q[t, h, :k] . w[h] | q[t, h, k:] rotated | zeros], w: [heads, k, n] (queries into the latent space:
+// k = the head's plain width, n = latent); qa: bfloat16 rows of ldq elements per (token, head).
+NIB_API int nib_head_product_kn(const float* q, int ldq_in, const void* w, const float* freq, float mag, const int* positions,
+                                void* qa, int ldq, int tokens, int heads, int n, int k, int rot, cudaStream_t stream) {
+    NIB_REQUIRE(nib_head_product_supported(1, k, n) == 1 && tokens >= 0 && heads > 0 && rot % 2 == 0 && ldq >= n + rot,
+                "per-head product: sizes k=%d n=%d are not supported", k, n);
+    if (tokens == 0) return 0;
+    const dim3 grid(ceil_div(tokens, LM_WARPS * 16), heads);
+    const int kp = (k + 15) / 16 * 16;
+#define NIB_HP(KP)                                                                                                                   \
+    if (kp == KP) {                                                                                                                  \
+        NIB_CUDA(launch_pdl(head_product_kn_kernel<KP>, grid, dim3(LM_WARPS * 32), (size_t)(KP * LTile<LM_BLOCK_N>::ROW_BYTES), stream, \
+                            q, ldq_in, (const __nv_bfloat16*)w, freq, mag, positions, (__nv_bfloat16*)qa, ldq, tokens, heads, n, k, rot)); \
+        return 0;                                                                                                                    \
+    }
+    NIB_HP(16) NIB_HP(32) NIB_HP(48) NIB_HP(64) NIB_HP(80) NIB_HP(96) NIB_HP(112) NIB_HP(128)
+#undef NIB_HP
+    NIB_REQUIRE(false, "per-head product: k=%d", k);
     return 0;
 }

@@ -83,7 +83,8 @@ class Kernels:
                      "nib_gemm_tc_qkv_supported", "nib_poly_norm", "nib_depth_mix", "nib_unary", "nib_head_norm_gate",
                      "nib_delta_rule_scan", "nib_causal_conv", "nib_rglru_scan", "nib_latent_store", "nib_latent_query",
                      "nib_latent_attention", "nib_latent_value", "nib_latent_attention_mma", "nib_latent_attention_mma_supported",
-                     "nib_latent_attention_mma_qwidth", "nib_block_diag_smallm", "nib_rmsnorm_pair", "nib_rmsnorm_pair_supported"):
+                     "nib_latent_attention_mma_qwidth", "nib_block_diag_smallm", "nib_rmsnorm_pair", "nib_rmsnorm_pair_supported", "nib_head_product_supported",
+                     "nib_head_product_nk", "nib_head_product_kn"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -720,6 +721,13 @@ class Kernels:
         if q32.shape[1] != heads * (dn + rot) or tuple(w_uk.shape) != (heads * dn, rank) or qa.shape[0] != m \
                 or qa.shape[1] != heads * ldq or ldq < rank + rot:
             raise KernelError("latent_query: shapes do not fit")
+        if qa.dtype == torch.bfloat16 and w_uk.dtype == torch.bfloat16 and m > 16 and not self.options.force_simt_gemm \
+                and self._lib.nib_head_product_supported(c_int(1), c_int(dn), c_int(rank)) == 1:
+            # more than a handful of tokens: one small product per head on the tensor cores
+            self._check(self._lib.nib_head_product_kn(_ptr(q32), c_int(q32.stride(0)), _ptr(w_uk), _ptr(freq32), c_float(mag), _ptr(positions),
+                                                      _ptr(qa), c_int(ldq), c_int(m), c_int(heads), c_int(rank), c_int(dn), c_int(rot),
+                                                      self._stream()), "latent_query (tensor cores)")
+            return
         self._check(self._lib.nib_latent_query(_ptr(q32), c_int(q32.stride(0)), _ptr(w_uk), _ptr(freq32), c_float(mag), _ptr(positions),
                                                _ptr(qa), c_int(ldq), c_int(_DT[qa.dtype]), c_int(m), c_int(heads), c_int(dn), c_int(rank),
                                                c_int(rot), c_int(_DT[w_uk.dtype]), self._stream()), "latent_query")
@@ -779,6 +787,11 @@ class Kernels:
         m = lat32.shape[0]
         if tuple(lat32.shape) != (m, heads * rank) or tuple(w_uv.shape) != (heads * dv, rank) or tuple(out.shape) != (m, heads * dv):
             raise KernelError("latent_value: shapes do not fit")
+        if w_uv.dtype == torch.bfloat16 and m > 16 and not self.options.force_simt_gemm \
+                and self._lib.nib_head_product_supported(c_int(0), c_int(rank), c_int(dv)) == 1:
+            self._check(self._lib.nib_head_product_nk(_ptr(lat32), c_int(lat32.stride(0)), _ptr(w_uv), _ptr(out), c_int(out.stride(0)), c_int(m),
+                                                      c_int(heads), c_int(dv), c_int(rank), self._stream()), "latent_value (tensor cores)")
+            return
         self._check(self._lib.nib_latent_value(_ptr(lat32), _ptr(w_uv), _ptr(out), c_int(out.stride(0)), c_int(m), c_int(heads),
                                                c_int(dv), c_int(rank), c_int(_DT[w_uv.dtype]), self._stream()), "latent_value")
 

@@ -55,8 +55,7 @@ __global__ void __launch_bounds__(DR_THREADS)
 delta_rule_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v, int ld,
                        const float* __restrict__ work, float* __restrict__ state, const int* __restrict__ q_start,
                        const int* __restrict__ slots, float* __restrict__ o, int ldo, int tokens, int heads, int d) {
-    pdl_launch_dependents();
-    pdl_wait();      // everything this kernel reads may come from the kernel before
+        pdl_wait();      // everything this kernel reads may come from the kernel before
     constexpr bool VEC = KR % 4 == 0;
     // a lane's slice, padded to an odd number of 16-byte units so that the eight lanes' 16-byte loads fall into distinct banks
     constexpr int KRP = (VEC && (KR / 4) % 2 == 0) ? KR + 4 : KR;
@@ -171,6 +170,7 @@ delta_rule_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
             prev_at = (long long)(t0 + c0 + t) * ldo + hoff + col;
         }
     }
+    pdl_launch_dependents();        // only now: blocks of the next kernel that became resident earlier would sit beside a long walk
     if (prev_at >= 0) {
 #pragma unroll
         for (int m = 1; m < DR_LPC; m <<= 1) out_prev += __shfl_xor_sync(0xffffffffu, out_prev, m);
@@ -195,12 +195,15 @@ NIB_API int nib_delta_rule_scan(const float* r, const float* k, const float* v, 
     if (requests == 0 || tokens == 0) return 0;
     NIB_CUDA(launch_pdl(delta_rule_prepare_kernel, dim3(ceil_div((long long)tokens * heads, 4)), dim3(128), (size_t)(0), stream, k, a_logit, ld, w_logit, ldw, work, tokens, heads, d));
     NIB_LAUNCH_CHECK();
+    // The walk is launched plainly, after the kernel before has ended: as a programmatic dependent its few blocks become
+    // resident while that kernel still runs, wherever room is first, several to an SM, and the walk of 2,048 tokens took
+    // 1.05 ms instead of 0.45 ms (heads of 64).
     const dim3 grid(ceil_div(d, DR_CV), heads, requests);
     const int kr = ceil_div(d, DR_LPC);
 #define NIB_DR(KR)                                                                                                         \
     if (kr <= KR) {                                                                                                        \
-        NIB_CUDA(launch_pdl(delta_rule_scan_kernel<KR>, dim3(grid), dim3(DR_THREADS), (size_t)(0), stream, r, k, v, ld, work, state, q_start, slots, o, ldo, tokens, \
-                                                                    heads, d));                                             \
+        delta_rule_scan_kernel<KR><<<grid, DR_THREADS, 0, stream>>>(r, k, v, ld, work, state, q_start, slots, o, ldo, tokens, \
+                                                                    heads, d);                                             \
         NIB_LAUNCH_CHECK();                                                                                                \
         return 0;                                                                                                          \
     }
@@ -295,8 +298,7 @@ template <typename T>
 __global__ void __launch_bounds__(LRU_WARPS * 32)
 rglru_scan_kernel(const float* __restrict__ work, const float* __restrict__ x, int ldx, float* __restrict__ state,
                   const int* __restrict__ q_start, const int* __restrict__ slots, T* __restrict__ out, int tokens, int width, int taps) {
-    pdl_launch_dependents();
-    pdl_wait();      // everything this kernel reads may come from the kernel before
+        pdl_wait();      // everything this kernel reads may come from the kernel before
     __shared__ float s_a[LRU_WARPS][32], s_b[LRU_WARPS][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + lane;
@@ -346,6 +348,7 @@ rglru_scan_kernel(const float* __restrict__ work, const float* __restrict__ x, i
             if (t + j < hi) Elem<T>::store(out + (size_t)(t0 + t + j) * width + c, S * gv[j]);
         }
     }
+    pdl_launch_dependents();        // only now: the next kernel's blocks would sit beside the walk
     if (warp != LRU_WARPS - 1) return;
     // the last warp leaves with the request's new state (empty segments are the identity map)
     st[c] = S;

@@ -268,6 +268,32 @@ def _query_rows(ops, values, dtype, heads, rank, rot):
     return qa.view(m, heads * qw), qa[:, :, :rank + rot].float().reshape(m, -1)
 
 
+@pytest.mark.parametrize("m", [70, 300])
+@pytest.mark.parametrize("heads,dn,rank,rot,dv", [(3, 8, 24, 8, 12), (16, 64, 128, 32, 64), (5, 48, 64, 16, 40), (2, 128, 192, 0, 128), (4, 20, 40, 8, 6)])
+def test_per_head_products_of_many_tokens(ops, m, heads, dn, rank, rot, dv):
+    """More than a handful of tokens take the tensor-core forms of the two maps between a head's space and the latent
+    space (bfloat16); against the plain statements."""
+    freq, mag = _freq(rot) if rot else (torch.zeros(0, device=DEV), 1.0)
+    positions = torch.arange(5, 5 + m, dtype=torch.int32, device=DEV)
+    q = rnd(m, heads * (dn + rot) + 3, seed=3)[:, :heads * (dn + rot)]
+    w_uk = rnd(heads * dn, rank, seed=4, scale=dn ** -0.5).to(torch.bfloat16)
+    qw, qdt = ops.latent_query_layout(torch.bfloat16, rank, rot)
+    qa = torch.full((m, heads * qw), 7.0, dtype=qdt, device=DEV)
+    ops.latent_query(q, w_uk, freq, mag, positions, qa, heads, dn, rank, rot)
+    qref = torch.empty(m, heads * (rank + rot))
+    TorchOps().latent_query(q.cpu(), w_uk.cpu(), freq.cpu(), mag, positions.cpu(), qref, heads, dn, rank, rot)
+    got = qa.view(m, heads, qw)
+    assert_close(got[:, :, :rank + rot].reshape(m, -1), qref, torch.bfloat16, "queries in the latent space")
+    assert (got[:, :, rank + rot:] == 0).all()
+    lat, w_uv = rnd(m, heads * rank, seed=5), rnd(heads * dv, rank, seed=6, scale=rank ** -0.5).to(torch.bfloat16)
+    wide = torch.empty(m, heads * dv + 8, dtype=torch.bfloat16, device=DEV)
+    out = wide[:, :heads * dv]
+    ops.latent_value(lat, w_uv, out, heads, dv, rank)
+    oref = torch.empty(m, heads * dv, dtype=torch.float64)
+    TorchOps().latent_value(lat.cpu(), w_uv.cpu(), oref, heads, dv, rank)
+    assert_close(out, oref, torch.bfloat16, "values out of the latent space")
+
+
 @pytest.mark.parametrize("dtype,general", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
 @pytest.mark.parametrize("window,page", [(0, 4), (5, 4), (32, 16), (33, 8), (64, 16), (200, 16)])
 @pytest.mark.parametrize("heads,rank,rot", [(3, 24, 8), (16, 64, 16), (20, 128, 32)])
