@@ -355,10 +355,12 @@ __device__ __forceinline__ void lm_a_from_f32(unsigned (&a)[4], const float* con
 
 // out[t, h, n] = sum_k a[t, h, k] * w[h, n, k] (w: [heads, n, k] bfloat16, its rows are the output features).
 // grid: (token tiles of 64, heads). a: floats, `lda` elements per token, the head's k values at h * k.
-template <int KP>
+// TO: bfloat16, or float with an optional bias [heads, n]. The head's n outputs of token t start at
+// out + t * ldo + h * out_head_stride.
+template <int KP, typename TO>
 __global__ void __launch_bounds__(LM_WARPS * 32)
-head_product_nk_kernel(const float* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, int ldo,
-                       int tokens, int n, int k) {
+head_product_nk_kernel(const float* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, const float* __restrict__ bias,
+                       TO* __restrict__ out, int ldo, long long out_head_stride, int tokens, int n, int k) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -392,11 +394,18 @@ head_product_nk_kernel(const float* __restrict__ a, int lda, const __nv_bfloat16
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             if (tok[r] >= tokens) continue;
-            __nv_bfloat16* o = out + (size_t)tok[r] * ldo + (size_t)h * n + n0;
+            TO* o = out + (size_t)tok[r] * ldo + (size_t)h * out_head_stride + n0;
 #pragma unroll
-            for (int j = 0; j < LM_BLOCK_N / 8; ++j)
-                if (n0 + j * 8 + 2 * t4 < n)
+            for (int j = 0; j < LM_BLOCK_N / 8; ++j) {
+                const int f = n0 + j * 8 + 2 * t4;
+                if (f >= n) continue;
+                if constexpr (sizeof(TO) == 2) {
                     *reinterpret_cast<unsigned*>(o + j * 8 + 2 * t4) = pack_bf16(s[j][2 * r], s[j][2 * r + 1]);
+                } else {
+                    const float b0 = bias ? bias[(size_t)h * n + f] : 0.f, b1 = bias ? bias[(size_t)h * n + f + 1] : 0.f;
+                    *reinterpret_cast<float2*>(o + j * 8 + 2 * t4) = make_float2(s[j][2 * r] + b0, s[j][2 * r + 1] + b1);
+                }
+            }
         }
     }
 }
@@ -509,17 +518,23 @@ NIB_API int nib_head_product_supported(int kn_layout, int k, int n) {
     return (k % 8 == 0 && k >= 8 && k <= 192 && n % 2 == 0 && n >= 2) ? 1 : 0;
 }
 
-// out[t, h, :n] = a[t, h, :k] . w[h]^T, w: [heads, n, k] (values out of the latent space: k = latent, n = value width).
-NIB_API int nib_head_product_nk(const float* a, int lda, const void* w, void* out, int ldo, int tokens, int heads, int n, int k,
-                                cudaStream_t stream) {
+// out[t, h, :n] = a[t, h, :k] . w[h]^T (+ bias[h]), w: [heads, n, k]: values out of the latent space (k = latent,
+// n = value width, bfloat16 out), or the gates of a block-diagonal map (float out with bias, out_f32 != 0). The head's
+// outputs of token t start at out + t * ldo + h * out_head_stride (elements).
+NIB_API int nib_head_product_nk(const float* a, int lda, const void* w, const float* bias, void* out, int ldo,
+                                long long out_head_stride, int out_f32, int tokens, int heads, int n, int k, cudaStream_t stream) {
     NIB_REQUIRE(nib_head_product_supported(0, k, n) == 1 && tokens >= 0 && heads > 0, "per-head product: sizes k=%d n=%d are not supported", k, n);
     if (tokens == 0) return 0;
     const dim3 grid(ceil_div(tokens, LM_WARPS * 16), heads);
     const int kp = (k + 15) / 16 * 16;
 #define NIB_HP(KP)                                                                                                                  \
     if (kp == KP) {                                                                                                                 \
-        NIB_CUDA(launch_pdl(head_product_nk_kernel<KP>, grid, dim3(LM_WARPS * 32), (size_t)LTile<KP>::BYTES, stream, a, lda,       \
-                            (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, tokens, n, k));                                     \
+        if (out_f32)                                                                                                                \
+            NIB_CUDA(launch_pdl(head_product_nk_kernel<KP, float>, grid, dim3(LM_WARPS * 32), (size_t)LTile<KP>::BYTES, stream, a, lda, \
+                                (const __nv_bfloat16*)w, bias, (float*)out, ldo, out_head_stride, tokens, n, k));                  \
+        else                                                                                                                        \
+            NIB_CUDA(launch_pdl(head_product_nk_kernel<KP, __nv_bfloat16>, grid, dim3(LM_WARPS * 32), (size_t)LTile<KP>::BYTES, stream, a, lda, \
+                                (const __nv_bfloat16*)w, bias, (__nv_bfloat16*)out, ldo, out_head_stride, tokens, n, k));          \
         return 0;                                                                                                                   \
     }
     NIB_HP(16) NIB_HP(32) NIB_HP(48) NIB_HP(64) NIB_HP(80) NIB_HP(96) NIB_HP(112) NIB_HP(128) NIB_HP(144) NIB_HP(160) NIB_HP(176) NIB_HP(192)

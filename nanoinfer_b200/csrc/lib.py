@@ -617,10 +617,12 @@ class Kernels:
                                                  _ptr(out), c_int(out.stride(0)), c_int(m), c_int(heads), c_int(d), c_float(eps),
                                                  c_int(_DT[out.dtype]), self._stream()), "head_norm_gate")
 
-    def block_diag_linear(self, a_blocks, w_blocks, bias32, out32):
+    def block_diag_linear(self, a_blocks, w_blocks, bias32, out32, a32=None):
         """out32[b] = a_blocks[b] . w_blocks[b]^T + bias32[b] for every block b: a_blocks [blocks, tokens, k],
-        w_blocks [blocks, n, k], bias32 [blocks, n] or None, out32 [blocks, tokens, n] floats. Up to 16 tokens take
-        one launch for all blocks (a decode step); more tokens run a product per block on the matrix kernels."""
+        w_blocks [blocks, n, k], bias32 [blocks, n] or None, out32 [blocks, tokens, n] floats. ``a32``: the same
+        activations as floats, token-major [tokens, blocks * k]. Up to 16 tokens take one launch for all blocks on the
+        CUDA cores (a decode step); more tokens take one launch on the tensor cores where the block size allows (from
+        ``a32``, rounded to bfloat16 on the way), else a product per block on the matrix kernels."""
         _need(a_blocks, None, "block_diag_linear a"); _need(w_blocks, a_blocks.dtype, "block_diag_linear w"); _need(out32, torch.float32, "block_diag_linear out")
         nb, m, k = a_blocks.shape
         n = w_blocks.shape[1]
@@ -631,6 +633,15 @@ class Kernels:
                 _need(bias32, torch.float32, "block_diag_linear bias")
             self._check(self._lib.nib_block_diag_smallm(_ptr(a_blocks), _ptr(w_blocks), _ptr(bias32), _ptr(out32), c_int(nb), c_int(m),
                                                         c_int(n), c_int(k), c_int(_DT[a_blocks.dtype]), self._stream()), "block-diagonal product (few tokens)")
+            return
+        if a32 is not None and w_blocks.dtype == torch.bfloat16 and not self.options.force_simt_gemm \
+                and self._lib.nib_head_product_supported(c_int(0), c_int(k), c_int(n)) == 1:
+            _need(a32, torch.float32, "block_diag_linear a32")
+            if tuple(a32.shape) != (m, nb * k):
+                raise KernelError("block_diag_linear: a32 does not fit")
+            self._check(self._lib.nib_head_product_nk(_ptr(a32), c_int(nb * k), _ptr(w_blocks), _ptr(bias32), _ptr(out32), c_int(n),
+                                                      c_longlong(m * n), c_int(1), c_int(m), c_int(nb), c_int(n), c_int(k), self._stream()),
+                        "block-diagonal product (tensor cores)")
             return
         for b in range(nb):
             self.linear(a_blocks[b], w_blocks[b], None if bias32 is None else bias32[b], out32[b], "f32")
@@ -789,8 +800,9 @@ class Kernels:
             raise KernelError("latent_value: shapes do not fit")
         if w_uv.dtype == torch.bfloat16 and m > 16 and not self.options.force_simt_gemm \
                 and self._lib.nib_head_product_supported(c_int(0), c_int(rank), c_int(dv)) == 1:
-            self._check(self._lib.nib_head_product_nk(_ptr(lat32), c_int(lat32.stride(0)), _ptr(w_uv), _ptr(out), c_int(out.stride(0)), c_int(m),
-                                                      c_int(heads), c_int(dv), c_int(rank), self._stream()), "latent_value (tensor cores)")
+            self._check(self._lib.nib_head_product_nk(_ptr(lat32), c_int(lat32.stride(0)), _ptr(w_uv), _ptr(None), _ptr(out), c_int(out.stride(0)),
+                                                      c_longlong(dv), c_int(0), c_int(m), c_int(heads), c_int(dv), c_int(rank), self._stream()),
+                        "latent_value (tensor cores)")
             return
         self._check(self._lib.nib_latent_value(_ptr(lat32), _ptr(w_uv), _ptr(out), c_int(out.stride(0)), c_int(m), c_int(heads),
                                                c_int(dv), c_int(rank), c_int(_DT[w_uv.dtype]), self._stream()), "latent_value")

@@ -69,7 +69,7 @@ class GatedLinearRecurrence(Mixer):
         u_blocks = torch.empty((self.blocks, m, self.bw), dtype=self.rt.dtype, device=dev)
         ops.causal_conv(xy32[:, :w], self.conv_w, self.conv_b, cache.state, 1, ctx, u32, u_blocks, self.taps, self.blocks)
         gates = torch.empty((self.blocks, m, 2 * self.bw), dtype=torch.float32, device=dev)
-        ops.block_diag_linear(u_blocks, self.w_gate, self.b_gate, gates)
+        ops.block_diag_linear(u_blocks, self.w_gate, self.b_gate, gates, a32=u32)
         out = torch.empty((m, w), dtype=self.rt.dtype, device=dev)
         ops.rglru_scan(u32, gates, xy32[:, w:], xy32[:, :w], self.softplus_lam, cache.state, ctx, out, self.taps, self.blocks)
         ops.linear(out, self.w_o, None, residual32, "add")

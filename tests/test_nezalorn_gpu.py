@@ -129,6 +129,11 @@ def test_block_diagonal_product(ops, dtype, blocks, m, n, k):
     ref = torch.empty(blocks, m, n)
     TorchOps().block_diag_linear(a.cpu(), w.cpu(), bias.cpu(), ref)
     assert_close(out, ref, torch.float32, "block-diagonal product")
+    # with the activations also given as floats, token-major (many tokens then take one launch on the tensor cores)
+    a32 = a.float().transpose(0, 1).reshape(m, blocks * k).contiguous()
+    out2 = torch.empty(blocks, m, n, device=DEV)
+    ops.block_diag_linear(a, w, bias, out2, a32=a32)
+    assert_close(out2, ref, torch.float32, "block-diagonal product from floats")
 
 
 # ------------------------------------------------------------------------------------------ generalized delta rule

@@ -122,7 +122,7 @@ class TorchOps:
         o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps)
         out.copy_((o.reshape(m, heads * d) * gain32.double() * torch.sigmoid(gate32.double())).to(out.dtype))
 
-    def block_diag_linear(self, a_blocks, w_blocks, bias32, out32):
+    def block_diag_linear(self, a_blocks, w_blocks, bias32, out32, a32=None):
         y = torch.einsum("bmk,bnk->bmn", a_blocks.double(), w_blocks.double())
         if bias32 is not None:
             y = y + bias32.double()[:, None, :]
