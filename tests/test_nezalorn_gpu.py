@@ -482,3 +482,35 @@ def test_greedy_generation_through_the_scheduler(folders):
             ids.append(int(row.argmax()))
         assert done[f"g{i}"] == ids[len(p):], i
     model.engine.cache.check()
+
+
+def test_command_line_tools_generate_and_serve(folders):
+    """bin/generate (with the cache and recomputing every token) and bin/serve as child processes, in 32-bit: the plain
+    implementation's greedy tokens."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def tool(name, argv):
+        done = subprocess.run([sys.executable, os.path.join(root, "bin", name)] + argv, capture_output=True, text=True, timeout=600)
+        assert done.returncode == 0, done.stderr[-2000:]
+        return [[int(t) for t in line.split("Completion: ", 1)[1].split()] for line in done.stdout.splitlines()
+                if line.startswith("Completion: ")]
+
+    def greedy(prompt, n):
+        ids = list(prompt)
+        for _ in range(n):
+            ids.append(int(plain_logits(folders["B"], ids)[-1].argmax()))
+        return ids[len(prompt):]
+
+    prompts = [tokens(9, 77, 41), tokens(26, 77, 42)]
+    common = ["--model-dir", folders["B"], "--dtype", "float32", "--block-size", "8", "--num-blocks", "32", "--max-tokens", "6"]
+    for extra in ([], ["--no-cache"]):
+        (got,) = tool("generate", common + ["--prompt", " ".join(map(str, prompts[0]))] + extra)
+        assert got == greedy(prompts[0], 6), extra
+    argv = common + ["--max-batch", "2", "--max-tokens-per-step", "16"]
+    for p in prompts:
+        argv += ["--prompt", " ".join(map(str, p))]
+    got = tool("serve", argv)
+    assert got == [greedy(p, 6) for p in prompts]
