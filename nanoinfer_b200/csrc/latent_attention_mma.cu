@@ -90,7 +90,7 @@ __device__ __forceinline__ void lm_pv(float (&o)[DVP / 8][4], const unsigned (&p
 // ------------------------------------------------------------------------------------------ prompt portions
 // grid: (row tiles of 64, requests). qa: [tokens, heads, DKP] bfloat16; out: [tokens, heads, rank] floats.
 template <int DKP, int DVP>
-__global__ void __launch_bounds__(LM_WARPS * 32)
+__global__ void __launch_bounds__(LM_WARPS * 32, DKP <= 160 ? 3 : 2)
 latent_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restrict__ out, const int* __restrict__ q_start,
                           const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride, int page_size,
                           const __nv_bfloat16* __restrict__ pages, int num_pages, int heads, int rank, int width, float scale, int window) {
@@ -99,7 +99,8 @@ latent_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qa, float* __restric
     const int req = blockIdx.y;
     const int row_begin = q_start[req], q_len = q_start[req + 1] - row_begin;
     const int rows_total = q_len * heads;
-    const int row0 = blockIdx.x * (LM_WARPS * 16);
+    // the tiles at a prompt's end see the most keys: they go first, the light ones fill the last wave
+    const int row0 = (gridDim.x - 1 - blockIdx.x) * (LM_WARPS * 16);
     if (row0 >= rows_total) return;
     const int pos0 = ctx_lens[req] - q_len;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2;

@@ -105,3 +105,42 @@ def plain_logits(folder, ids):
 def tokens(n, vocab, seed):
     g = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def random_config(rng):
+    """A configuration with random layer order, sizes (odd ones, ones, sizes no kernel's fast path takes) and constants."""
+    width = rng.choice([40, 64, 72, 100, 128, 192, 258, 320])
+    vocab = rng.choice([50, 131, 257, 448, 1000])
+    n_layers = rng.randint(2, 9)
+    layers, owners = [], []
+    for i in range(n_layers):
+        kind = rng.choice(["latent", "delta", "lru"])
+        ff = rng.choice([None, 48, 96, 130, 256, 300])
+        if kind == "delta":
+            layer = delta(rng.choice([1, 2, 3, 4, 6]), rng.choice([8, 12, 16, 20, 24, 32, 40, 48, 64, 72, 96, 128]))
+        elif kind == "lru":
+            blocks = rng.choice([1, 2, 3, 4, 8])
+            layer = lru(blocks * rng.choice([4, 8, 12, 16, 20, 32, 64]), rng.choice([1, 2, 3, 4, 5, 7]), blocks)
+        else:
+            rot_dim = rng.choice([2, 4, 8, 12, 16, 32, 64])
+            scaling = rng.choice([None, {"factor": rng.choice([2.0, 4.0, 8.0, 32.0]), "original": rng.choice([16, 64, 1024, 4096]),
+                                         "fast": rng.choice([8.0, 32.0]), "slow": rng.choice([0.5, 1.0, 2.0])}])
+            rot = {"dims": rot_dim, "base": rng.choice([100.0, 10000.0, 20000.0, 1e6])}
+            if scaling: rot["scaling"] = scaling
+            kv_rank = rng.choice([8, 12, 16, 20, 24, 32, 48, 64, 80, 96, 128, 160, 200, 256])
+            window = rng.choice([1, 2, 3, 5, 16, 17, 31, 32, 33, 63, 64, 65, 100, 136, 500])
+            heads = rng.choice([1, 2, 3, 4, 6, 8, 16, 17, 20])
+            dim, vdim, q_rank = rng.choice([4, 8, 16, 24, 32, 48, 64, 136]), rng.choice([3, 4, 8, 16, 32, 48, 64]), rng.choice([8, 16, 24, 48, 128])
+            src = None
+            if owners and rng.random() < 0.4:
+                src = rng.choice(owners)
+                o = layers[src]["mixer"]
+                layer = latent(heads, dim, o["rot_dim"], vdim, q_rank, o["kv_rank"], window, rot=o["rot"], kv_from=src, scale=rng.choice([None, 0.1, 0.3]))
+            else:
+                layer = latent(heads, dim, rot_dim, vdim, q_rank, kv_rank, window, rot=rot, scale=rng.choice([None, 0.1, 0.3]))
+                owners.append(i)
+        layers.append(with_mlp(layer, ff))
+    for layer in layers:
+        if layer["type"] == "general_delta":
+            layer["mixer"]["decay_rank"] = rng.choice([1, 4, 8, 16, 24, 64])
+    return {"architecture": "Nezalorn", "vocab": vocab, "width": width, "norm": {"eps": rng.choice([1e-6, 1e-5, 1e-4])}, "layers": layers}

@@ -484,6 +484,39 @@ def test_greedy_generation_through_the_scheduler(folders):
     model.engine.cache.check()
 
 
+@pytest.mark.parametrize("seed", [100, 101, 103, 107, 112])
+def test_random_configurations_in_32_bit(seed, tmp_path):
+    """Layer orders, sizes and constants drawn at random (heads of 17, latents of 200, windows of 1, one tap, widths that
+    no vector path takes ...): a prompt in portions with a decoded tail beside a second request, against the plain
+    implementation."""
+    import random
+    from nezalorn_util import random_config
+    from nanoinfer_b200.engine import StepEntry
+    rng = random.Random(seed)
+    cfg = random_config(rng)
+    d = write_model(str(tmp_path), cfg, seed, strip_rank=seed % 2 == 0)
+    n = 70
+    ids, other = tokens(n, cfg["vocab"], seed), tokens(33, cfg["vocab"], seed + 1)
+    ref, ref2 = plain_logits(d, ids), plain_logits(d, other)
+    eng = gpu_engine(d, "float32", page=rng.choice([4, 16]), pages=64, slots=2)
+    a, b = eng.open("a"), eng.open("b")
+    got, got2, pos, pos2 = [], [], 0, 0
+    for c in [17, 2, 1, 30, 3, 11] + [1] * 6:
+        entries = [StepEntry(a, ids[pos:pos + c], list(range(c)))]
+        m = min(len(other) - pos2, max(1, c // 2))
+        if m > 0:
+            entries.insert(0, StepEntry(b, other[pos2:pos2 + m], list(range(m))))
+        lg = eng.step(entries).clone()
+        if m > 0:
+            got2.append(lg[:m]); lg = lg[m:]; pos2 += m
+        got.append(lg); pos += c
+    assert pos == n
+    assert_close(torch.cat(got), ref, torch.float32, "first request")
+    assert_close(torch.cat(got2), ref2[:pos2], torch.float32, "second request")
+    eng.check_device()
+    eng.cache.check()
+
+
 def test_command_line_tools_generate_and_serve(folders):
     """bin/generate (with the cache and recomputing every token) and bin/serve as child processes, in 32-bit: the plain
     implementation's greedy tokens."""
