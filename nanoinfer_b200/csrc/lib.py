@@ -84,7 +84,7 @@ class Kernels:
                      "nib_delta_rule_scan", "nib_causal_conv", "nib_rglru_scan", "nib_latent_store", "nib_latent_query",
                      "nib_latent_attention", "nib_latent_value", "nib_latent_attention_mma", "nib_latent_attention_mma_supported",
                      "nib_latent_attention_mma_qwidth", "nib_block_diag_smallm", "nib_rmsnorm_pair", "nib_rmsnorm_pair_supported", "nib_head_product_supported",
-                     "nib_head_product_nk", "nib_head_product_kn"):
+                     "nib_head_product_nk", "nib_head_product_kn", "nib_depth_mix_norm_pair"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -597,6 +597,22 @@ class Kernels:
         self._check(self._lib.nib_depth_mix(_ptr(hist32), _ptr(x32), _ptr(coef32), c_int(n), c_longlong(x32.numel()),
                                             self._stream()), "depth_mix")
 
+    def depth_mix_norm_pair(self, hist32, x32, coef32, n, gain_a32, gain_b32, eps, out_a, out_b):
+        """``depth_mix`` followed by ``rmsnorm_pair`` of the new x32, in one pass over the rows where the width allows."""
+        if self._lib.nib_rmsnorm_pair_supported(c_int(x32.shape[1])) != 1:
+            self.depth_mix(hist32, x32, coef32, n)
+            self.rmsnorm_pair(x32, gain_a32, gain_b32, eps, out_a, out_b)
+            return
+        _need(hist32, torch.float32, "depth_mix history"); _need(x32, torch.float32, "depth_mix x"); _need(coef32, torch.float32, "depth_mix coefficients")
+        _need(gain_a32, torch.float32, "gain"); _need(gain_b32, torch.float32, "gain"); _need(out_a, None, "norm out"); _need(out_b, out_a.dtype, "norm out")
+        rows, hidden = x32.shape
+        if hist32.shape[0] < n or tuple(hist32.shape[1:]) != (rows, hidden) or coef32.numel() < n or tuple(out_a.shape) != (rows, hidden) \
+                or tuple(out_b.shape) != (rows, hidden) or gain_a32.numel() != hidden or gain_b32.numel() != hidden:
+            raise KernelError("depth_mix_norm_pair: shapes do not fit")
+        self._check(self._lib.nib_depth_mix_norm_pair(_ptr(hist32), _ptr(x32), _ptr(coef32), c_int(n), _ptr(gain_a32), _ptr(gain_b32),
+                                                      _ptr(out_a), _ptr(out_b), c_int(rows), c_int(hidden), c_float(eps), c_int(_DT[out_a.dtype]),
+                                                      self._stream()), "depth_mix + rmsnorm (two gains)")
+
     def unary(self, in32, out, kind):
         """out = f(in32) element by element with a change of storage type; kind: 'tanh' | 'copy' | 'sigmoid'."""
         self._rows(in32, torch.float32, "unary in"); self._rows(out, None, "unary out")
@@ -732,9 +748,10 @@ class Kernels:
         if q32.shape[1] != heads * (dn + rot) or tuple(w_uk.shape) != (heads * dn, rank) or qa.shape[0] != m \
                 or qa.shape[1] != heads * ldq or ldq < rank + rot:
             raise KernelError("latent_query: shapes do not fit")
-        if qa.dtype == torch.bfloat16 and w_uk.dtype == torch.bfloat16 and m > 16 and not self.options.force_simt_gemm \
+        if qa.dtype == torch.bfloat16 and w_uk.dtype == torch.bfloat16 and not self.options.force_simt_gemm \
                 and self._lib.nib_head_product_supported(c_int(1), c_int(dn), c_int(rank)) == 1:
-            # more than a handful of tokens: one small product per head on the tensor cores
+            # one small product per head on the tensor cores (the warp-per-row form walks a head's matrix row by row, one
+            # round trip to memory each: 40-80 us for the 8 tokens of a decode step at heads of 128)
             self._check(self._lib.nib_head_product_kn(_ptr(q32), c_int(q32.stride(0)), _ptr(w_uk), _ptr(freq32), c_float(mag), _ptr(positions),
                                                       _ptr(qa), c_int(ldq), c_int(m), c_int(heads), c_int(rank), c_int(dn), c_int(rot),
                                                       self._stream()), "latent_query (tensor cores)")
@@ -798,7 +815,7 @@ class Kernels:
         m = lat32.shape[0]
         if tuple(lat32.shape) != (m, heads * rank) or tuple(w_uv.shape) != (heads * dv, rank) or tuple(out.shape) != (m, heads * dv):
             raise KernelError("latent_value: shapes do not fit")
-        if w_uv.dtype == torch.bfloat16 and m > 16 and not self.options.force_simt_gemm \
+        if w_uv.dtype == torch.bfloat16 and not self.options.force_simt_gemm \
                 and self._lib.nib_head_product_supported(c_int(0), c_int(rank), c_int(dv)) == 1:
             self._check(self._lib.nib_head_product_nk(_ptr(lat32), c_int(lat32.stride(0)), _ptr(w_uv), _ptr(None), _ptr(out), c_int(out.stride(0)),
                                                       c_longlong(dv), c_int(0), c_int(m), c_int(heads), c_int(dv), c_int(rank), self._stream()),

@@ -360,6 +360,41 @@ rglru_scan_kernel(const float* __restrict__ work, const float* __restrict__ x, i
     for (int j = 0; j < taps - 1; ++j) st[(size_t)(1 + j) * width + c] = keep[j];
 }
 
+// A handful of tokens (a decode step): gates, decay and walk in one kernel, one thread per (request, channel).
+template <typename T>
+__global__ void __launch_bounds__(128)
+rglru_few_tokens_kernel(const float* __restrict__ u32, const float* __restrict__ gates, const float* __restrict__ y_logit, int ldy,
+                        const float* __restrict__ x, int ldx, const float* __restrict__ softplus_lam, float* __restrict__ state,
+                        const int* __restrict__ q_start, const int* __restrict__ slots, T* __restrict__ out, int tokens, int width,
+                        int taps, int blocks) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    const int req = blockIdx.y;
+    const int t0 = q_start[req], n = q_start[req + 1] - t0;
+    float* st = state + (size_t)slots[req] * taps * width;
+    const int bw = width / blocks, b = c / bw, cb = c % bw;
+    const float* g = gates + ((size_t)b * tokens) * 2 * bw + cb;
+    const float sp = softplus_lam[c];
+    float S = st[c];
+    for (int t = 0; t < n; ++t) {
+        const size_t row = (size_t)(t0 + t);
+        const float rg = sigmoidf_(g[row * 2 * bw]), ig = sigmoidf_(g[row * 2 * bw + bw]);
+        const float log_a = -8.0f * rg * sp;
+        S = fmaf(expf(log_a), S, sqrtf(fmaxf(0.f, -expm1f(2.0f * log_a))) * (ig * u32[row * width + c]));
+        const float z = y_logit[row * ldy + c];
+        Elem<T>::store(out + row * width + c, S * (0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)))));
+    }
+    st[c] = S;
+    float keep[LRU_MAX_TAPS];
+    for (int j = 0; j < taps - 1; ++j) {
+        const int src = n - (taps - 1) + j;
+        keep[j] = src >= 0 ? x[(size_t)(t0 + src) * ldx + c] : st[(size_t)(1 + j + n) * width + c];
+    }
+    for (int j = 0; j < taps - 1; ++j) st[(size_t)(1 + j) * width + c] = keep[j];
+}
+
 // work: [3, tokens, width] floats of scratch.
 NIB_API int nib_rglru_scan(const float* u32, const float* gates, const float* y_logit, int ldy, const float* x, int ldx,
                            const float* softplus_lam, float* state, const int* q_start, const int* slots, void* out, float* work,
@@ -368,6 +403,16 @@ NIB_API int nib_rglru_scan(const float* u32, const float* gates, const float* y_
                 "rglru_scan: bad sizes (width %d, taps %d of at most %d, blocks %d)", width, taps, LRU_MAX_TAPS, blocks);
     NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "rglru_scan: unknown dtype %d", dtype);
     if (requests == 0 || tokens == 0) return 0;
+    if (tokens <= 16) {         // which kernel runs depends on the step's size alone
+        const dim3 few(ceil_div(width, 128), requests);
+        if (dtype == NIB_F32)
+            NIB_CUDA(launch_pdl(rglru_few_tokens_kernel<float>, few, dim3(128), (size_t)0, stream, u32, gates, y_logit, ldy, x, ldx,
+                                softplus_lam, state, q_start, slots, (float*)out, tokens, width, taps, blocks));
+        else
+            NIB_CUDA(launch_pdl(rglru_few_tokens_kernel<__nv_bfloat16>, few, dim3(128), (size_t)0, stream, u32, gates, y_logit, ldy, x,
+                                ldx, softplus_lam, state, q_start, slots, (__nv_bfloat16*)out, tokens, width, taps, blocks));
+        return 0;
+    }
     NIB_CUDA(launch_pdl(rglru_gate_kernel, dim3(ceil_div((long long)tokens * width, 256)), dim3(256), (size_t)(0), stream, u32, gates, y_logit, ldy, softplus_lam, work,
                                                                                     tokens, width, blocks));
     NIB_LAUNCH_CHECK();

@@ -10,7 +10,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts.base import CacheNeed, LayerCache, Runtime, StateNeed, StepContext, normed_input
+from ..parts.base import CacheNeed, LayerCache, Runtime, StateNeed, StepContext, normed_input, resolve_pending
 from ..parts.spec import ModelPlan, PartSpec
 from ..registry import get_arrangement, get_part
 
@@ -99,7 +99,11 @@ class DecoderModel:
         for pos in self.positions.values():
             pos.add_to_embedding(x32, ctx)
         for i, e in enumerate(self.schedule):
-            self.layers[e.layer].forward(x32, ctx, caches[i])
+            layer = self.layers[e.layer]
+            if not getattr(layer, "resolves_pending", False):
+                resolve_pending(x32, ctx)       # work that the layer before left to the stream's next reader
+            layer.forward(x32, ctx, caches[i])
+        resolve_pending(x32, ctx)
         if want_rows is None or want_rows.numel() == 0:
             return None
         if ctx.all_rows_wanted:

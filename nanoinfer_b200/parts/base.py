@@ -120,6 +120,19 @@ class StepContext:
     scratch: Dict[str, object] = field(default_factory=dict)  # what parts of one step hand to later parts of the same step
 
 
+# Key of ``StepContext.scratch`` under which a part may leave work on the residual stream that it has NOT done yet (an
+# object with ``run(x32, ctx)``): the next reader of the stream pops it and runs it first, or folds it into its own
+# first kernel. The decoder runs what is left before a layer that does not look for it and before the final norm.
+PENDING_STREAM_OP = "stream.pending"
+
+
+def resolve_pending(x32: torch.Tensor, ctx: "StepContext") -> None:
+    """Run the work that an earlier part left pending on the stream, if any."""
+    op = ctx.scratch.pop(PENDING_STREAM_OP, None)
+    if op is not None:
+        op.run(x32, ctx)
+
+
 @dataclass
 class LayerCache:
     """The cache of one schedule entry, as its mixer sees it."""

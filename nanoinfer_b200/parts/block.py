@@ -14,7 +14,7 @@ from typing import Dict
 import torch
 
 from ..registry import register_arrangement
-from .base import LayerCache, StepContext, normed_input
+from .base import PENDING_STREAM_OP, LayerCache, StepContext, normed_input
 
 
 class PreNormBlock:
@@ -38,6 +38,8 @@ class ParallelBlock:
     ``begin(x32, ctx)`` before and ``forward(x32, ctx)`` after the layer: what goes on is a mix of this and earlier
     results). Both norms are computed before either branch adds to the stream."""
 
+    resolves_pending = True     # it looks for work left pending on the stream itself (and may fold it into its norms)
+
     def __init__(self, parts: Dict[str, object]):
         self.mixer_norm, self.mixer = parts["mixer_norm"], parts["mixer"]
         self.ffn_norm, self.ffn = parts.get("ffn_norm"), parts.get("ffn")
@@ -48,7 +50,14 @@ class ParallelBlock:
 
     def forward(self, x32: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
         together = getattr(self.mixer_norm, "forward_with", None) if type(self.mixer_norm) is type(self.ffn_norm) else None
-        if together is not None:        # two norms of one kind: the stream is read once
+        pending = ctx.scratch.pop(PENDING_STREAM_OP, None)      # what the layer before left to do on the stream
+        fused = pending is not None and together is not None and hasattr(pending, "run_with_norms") \
+            and self.mixer_norm.size == self.ffn_norm.size and self.mixer_norm.eps == self.ffn_norm.eps
+        if pending is not None and not fused:
+            pending.run(x32, ctx)
+        if fused:                       # the pending sum and both norms in one pass over the rows
+            h_mixer, h_ffn = pending.run_with_norms(x32, ctx, self.mixer_norm, self.ffn_norm)
+        elif together is not None:      # two norms of one kind: the stream is read once
             h_mixer, h_ffn = together(self.ffn_norm, x32)
         else:
             h_mixer = self.mixer_norm.forward(x32)

@@ -11,7 +11,7 @@ from typing import Dict
 import torch
 
 from ..registry import register_part
-from .base import Part, Runtime, StepContext
+from .base import PENDING_STREAM_OP, Part, Runtime, StepContext
 from .spec import PartSpec, TensorSpec
 
 _KEY = "depth_average.history"
@@ -43,8 +43,20 @@ class DepthAverage(Part):
             ctx.scratch[_KEY] = hist
 
     def forward(self, x32: torch.Tensor, ctx: StepContext) -> None:
-        """After the layer: x32 (the layer's result) joins the streams and is replaced by their weighted sum."""
+        """After the layer: x32 (the layer's result) is to join the streams and to be replaced by their weighted sum. The
+        work is left pending in the step's context (``parts.base.PENDING_STREAM_OP``): whoever reads the stream next
+        either runs it (``run``) or, if it norms the stream twice anyway, lets one kernel do both (``run_with_norms``)."""
+        ctx.scratch[PENDING_STREAM_OP] = self
+
+    def run(self, x32: torch.Tensor, ctx: StepContext) -> None:
         self.ops.depth_mix(ctx.scratch[_KEY], x32, self.coef, self.inputs)
+
+    def run_with_norms(self, x32: torch.Tensor, ctx: StepContext, norm_a, norm_b):
+        """The pending sum and the two RMS norms of its result (equal size and eps) in one pass; returns (h_a, h_b)."""
+        a = torch.empty((x32.shape[0], norm_a.size), dtype=self.rt.dtype, device=x32.device)
+        b = torch.empty_like(a)
+        self.ops.depth_mix_norm_pair(ctx.scratch[_KEY], x32, self.coef, self.inputs, norm_a.gain, norm_b.gain, norm_a.eps, a, b)
+        return a, b
 
 
 register_part("depth_average", DepthAverage)

@@ -82,6 +82,22 @@ def test_two_norms_of_one_row(ops, dtype, rows, width):
     assert_close(b, base * gb.double(), dtype, "second norm")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,width", [(1, 64), (9, 1000), (3, 4096), (5, 90)])
+def test_depth_mix_and_two_norms_in_one_pass(ops, dtype, rows, width):
+    hist, x = rnd(4, rows, width, seed=2), rnd(rows, width, seed=3)
+    coef, ga, gb = torch.tensor([0.5, -0.25, 1.5], device=DEV), rnd(width, seed=4), rnd(width, seed=5)
+    h_ref, x_ref = hist.cpu().clone(), x.cpu().clone()
+    a_ref, b_ref = torch.empty(rows, width, dtype=torch.float64), torch.empty(rows, width, dtype=torch.float64)
+    TorchOps().depth_mix_norm_pair(h_ref, x_ref, coef.cpu(), 3, ga.cpu(), gb.cpu(), 1e-5, a_ref, b_ref)
+    a, b = torch.empty(rows, width, dtype=dtype, device=DEV), torch.empty(rows, width, dtype=dtype, device=DEV)
+    ops.depth_mix_norm_pair(hist, x, coef, 3, ga, gb, 1e-5, a, b)
+    assert_close(x, x_ref, torch.float32, "weighted sum")
+    assert_close(hist, h_ref, torch.float32, "streams")
+    assert_close(a, a_ref, dtype, "first norm")
+    assert_close(b, b_ref, dtype, "second norm")
+
+
 @pytest.mark.parametrize("shape", [(7, 33), (16, 64)])
 def test_depth_mix_other_shapes(ops, shape):
     hist, x = rnd(3, *shape, seed=2), rnd(*shape, seed=3)
@@ -273,11 +289,11 @@ def _query_rows(ops, values, dtype, heads, rank, rot):
     return qa.view(m, heads * qw), qa[:, :, :rank + rot].float().reshape(m, -1)
 
 
-@pytest.mark.parametrize("m", [70, 300])
+@pytest.mark.parametrize("m", [1, 8, 70, 300])
 @pytest.mark.parametrize("heads,dn,rank,rot,dv", [(3, 8, 24, 8, 12), (16, 64, 128, 32, 64), (5, 48, 64, 16, 40), (2, 128, 192, 0, 128), (4, 20, 40, 8, 6)])
-def test_per_head_products_of_many_tokens(ops, m, heads, dn, rank, rot, dv):
-    """More than a handful of tokens take the tensor-core forms of the two maps between a head's space and the latent
-    space (bfloat16); against the plain statements."""
+def test_per_head_products_on_the_tensor_cores(ops, m, heads, dn, rank, rot, dv):
+    """The tensor-core forms of the two maps between a head's space and the latent space (bfloat16 weights, rows for the
+    tensor-core attention), from one token to hundreds; against the plain statements."""
     freq, mag = _freq(rot) if rot else (torch.zeros(0, device=DEV), 1.0)
     positions = torch.arange(5, 5 + m, dtype=torch.int32, device=DEV)
     q = rnd(m, heads * (dn + rot) + 3, seed=3)[:, :heads * (dn + rot)]

@@ -112,6 +112,10 @@ class TorchOps:
             acc += coef32[j].double() * hist32[j].double()
         x32.copy_(acc.to(torch.float32))
 
+    def depth_mix_norm_pair(self, hist32, x32, coef32, n, gain_a32, gain_b32, eps, out_a, out_b):
+        self.depth_mix(hist32, x32, coef32, n)
+        self.rmsnorm_pair(x32, gain_a32, gain_b32, eps, out_a, out_b)
+
     def unary(self, in32, out, kind):
         x = in32.double()
         out.copy_({"tanh": torch.tanh, "copy": lambda v: v, "sigmoid": torch.sigmoid}[kind](x).to(out.dtype))
