@@ -304,6 +304,68 @@ depth_mix_norm_pair_kernel(float* __restrict__ hist, float* __restrict__ x, cons
     }
 }
 
+// The same for a handful of rows (a decode step): a block of 256 threads per row, so that a row's streams are fetched
+// by 256 threads at once instead of by one warp; four streams in flight per thread.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+depth_mix_norm_pair_row_kernel(float* __restrict__ hist, float* __restrict__ x, const float* __restrict__ coef, int n,
+                               const float* __restrict__ gain_a, const float* __restrict__ gain_b, T* __restrict__ out_a,
+                               T* __restrict__ out_b, int n_rows, int hidden, float eps) {
+    __shared__ float part[8];
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const int n4 = hidden >> 2;
+    const size_t stream4 = (size_t)n_rows * n4;
+    float4* xr = reinterpret_cast<float4*>(x) + (size_t)r * n4;
+    float4* hr = reinterpret_cast<float4*>(hist) + (size_t)r * n4;
+    float4 v[NV], newest[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = tid + 256 * i;
+        newest[i] = c < n4 ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll 4
+    for (int j = 0; j < n - 1; ++j) {           // ascending j, as everywhere
+        const float cj = coef[j];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = tid + 256 * i;
+            const float4 h = c < n4 ? hr[(size_t)j * stream4 + c] : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[i].x = fmaf(cj, h.x, v[i].x); v[i].y = fmaf(cj, h.y, v[i].y);
+            v[i].z = fmaf(cj, h.z, v[i].z); v[i].w = fmaf(cj, h.w, v[i].w);
+        }
+    }
+    const float c_new = coef[n - 1];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = tid + 256 * i;
+        v[i].x = fmaf(c_new, newest[i].x, v[i].x); v[i].y = fmaf(c_new, newest[i].y, v[i].y);
+        v[i].z = fmaf(c_new, newest[i].z, v[i].z); v[i].w = fmaf(c_new, newest[i].w, v[i].w);
+        if (c < n4) {
+            hr[(size_t)(n - 1) * stream4 + c] = newest[i];
+            xr[c] = v[i];
+            ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+            ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    }
+    ss = block_sum_256(ss, part);
+    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = tid + 256 * i;
+        if (c >= n4) continue;
+        const float4 ga = __ldg(reinterpret_cast<const float4*>(gain_a) + c), gb = __ldg(reinterpret_cast<const float4*>(gain_b) + c);
+        const float sx = v[i].x * scale, sy = v[i].y * scale, sz = v[i].z * scale, sw = v[i].w * scale;
+        T* oa = out_a + (size_t)r * hidden + 4 * c;
+        T* ob = out_b + (size_t)r * hidden + 4 * c;
+        Elem<T>::store(oa, sx * ga.x); Elem<T>::store(oa + 1, sy * ga.y); Elem<T>::store(oa + 2, sz * ga.z); Elem<T>::store(oa + 3, sw * ga.w);
+        Elem<T>::store(ob, sx * gb.x); Elem<T>::store(ob + 1, sy * gb.y); Elem<T>::store(ob + 2, sz * gb.z); Elem<T>::store(ob + 3, sw * gb.w);
+    }
+}
+
 // Takes the widths nib_rmsnorm_pair takes (nib_rmsnorm_pair_supported).
 NIB_API int nib_depth_mix_norm_pair(float* hist, float* x, const float* coef, int n, const float* gain_a, const float* gain_b,
                                     void* out_a, void* out_b, int n_rows, int hidden, float eps, int dtype, cudaStream_t stream) {
@@ -311,6 +373,16 @@ NIB_API int nib_depth_mix_norm_pair(float* hist, float* x, const float* coef, in
     NIB_REQUIRE(dtype == NIB_F32 || dtype == NIB_BF16, "depth_mix_norm_pair: unknown dtype %d", dtype);
     NIB_REQUIRE((((uintptr_t)hist | (uintptr_t)x | (uintptr_t)gain_a | (uintptr_t)gain_b) & 15) == 0, "depth_mix_norm_pair: 16-byte boundaries");
     if (n_rows == 0) return 0;
+    if (n_rows <= 32) {         // which kernel runs depends on the step's size alone
+#define NIB_DR(T, NV) NIB_CUDA(launch_pdl(depth_mix_norm_pair_row_kernel<T, NV>, dim3(n_rows), dim3(256), (size_t)0, stream, hist, x, coef, n, gain_a, gain_b, (T*)out_a, (T*)out_b, n_rows, hidden, eps))
+        if (dtype == NIB_F32) {
+            if (hidden <= 1024) NIB_DR(float, 1); else if (hidden <= 2048) NIB_DR(float, 2); else NIB_DR(float, 4);
+        } else {
+            if (hidden <= 1024) NIB_DR(__nv_bfloat16, 1); else if (hidden <= 2048) NIB_DR(__nv_bfloat16, 2); else NIB_DR(__nv_bfloat16, 4);
+        }
+#undef NIB_DR
+        return 0;
+    }
     const int warps = n_rows >= 8 ? 8 : n_rows;
     const dim3 grid(ceil_div(n_rows, warps)), block(32 * warps);
 #define NIB_DP(T, NV) NIB_CUDA(launch_pdl(depth_mix_norm_pair_kernel<T, NV>, grid, block, (size_t)0, stream, hist, x, coef, n, gain_a, gain_b, (T*)out_a, (T*)out_b, n_rows, hidden, eps))

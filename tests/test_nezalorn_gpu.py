@@ -83,7 +83,7 @@ def test_two_norms_of_one_row(ops, dtype, rows, width):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rows,width", [(1, 64), (9, 1000), (3, 4096), (5, 90)])
+@pytest.mark.parametrize("rows,width", [(1, 64), (9, 1000), (3, 4096), (5, 90), (40, 64), (33, 2048), (70, 3000)])
 def test_depth_mix_and_two_norms_in_one_pass(ops, dtype, rows, width):
     hist, x = rnd(4, rows, width, seed=2), rnd(rows, width, seed=3)
     coef, ga, gb = torch.tensor([0.5, -0.25, 1.5], device=DEV), rnd(width, seed=4), rnd(width, seed=5)
