@@ -479,6 +479,22 @@ def test_long_decoding_through_captured_graphs_passes_windows_and_pages(folders)
         assert_close(torch.stack(got[i]), plain_logits(folders["A"], seqs[i]), torch.float32, f"request {i}")
 
 
+def test_prompt_portions_replayed_from_a_captured_graph(folders):
+    """Portions of one recurring shape are captured the third time the shape is seen and replayed from then on: states,
+    latents and the depth average's streams must go on through captured steps as through eager ones."""
+    from nanoinfer_b200.engine import StepEntry
+    eng = gpu_engine(folders["A"], "float32", page=4, pages=64, slots=2)
+    assert eng._portion_graphs is not None
+    eng._portion_graphs.min_tokens = 8
+    ids = tokens(96, 131, 77)
+    rc = eng.open("p")
+    got = [eng.step([StepEntry(rc, ids[i:i + 8], list(range(8)))]).clone() for i in range(0, 96, 8)]
+    assert eng._portion_graphs.captured and eng.graph_launches > 0
+    assert_close(torch.cat(got), plain_logits(folders["A"], ids), torch.float32, "portions through a graph")
+    eng.close(rc)
+    eng.cache.check()
+
+
 def test_greedy_generation_through_the_scheduler(folders):
     from nanoinfer_b200.api import Model
     from nanoinfer_b200.config import EngineConfig
