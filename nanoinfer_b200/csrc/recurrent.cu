@@ -226,9 +226,8 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, int ldx, const f
                                    float* __restrict__ u32, T* __restrict__ u_blocks, int tokens, int width, int taps, int blocks) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (long long)tokens * width) return;
-    const int t = (int)(i / width), c = (int)(i % width);
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;       // a token per block row: no division per element
+    if (c >= width) return;
     const int req = req_index[t];
     const int local = t - q_start[req];
     const float* hist = state + ((size_t)slots[req] * rows_per_slot + hist_row0) * width;
@@ -248,7 +247,7 @@ NIB_API int nib_causal_conv(const float* x, int ldx, const float* w, const float
                             void* u_blocks, int tokens, int width, int taps, int blocks, int dtype, cudaStream_t stream) {
     NIB_REQUIRE(tokens >= 0 && width > 0 && taps >= 1 && blocks >= 1 && width % blocks == 0, "causal_conv: bad sizes");
     if (tokens == 0) return 0;
-    const int grid = ceil_div((long long)tokens * width, 256);
+    const dim3 grid(tokens, ceil_div(width, 256));
     if (dtype == NIB_F32)
         NIB_CUDA(launch_pdl(causal_conv_kernel<float>, dim3(grid), dim3(256), (size_t)(0), stream, x, ldx, w, bias, state, rows_per_slot, hist_row0, q_start, req_index,
                                                             slots, u32, (float*)u_blocks, tokens, width, taps, blocks));
@@ -272,7 +271,7 @@ NIB_API int nib_causal_conv(const float* x, int ldx, const float* w, const float
 // and writes S * g. Loads are issued eight tokens ahead. State row 0 is S, rows 1.. the last taps-1 inputs x of the
 // convolution (row stride ldx), renewed here.
 constexpr int LRU_MAX_TAPS = 16;
-constexpr int LRU_WARPS = 16;
+constexpr int LRU_WARPS = 32;
 constexpr int LRU_AHEAD = 8;
 
 __global__ void rglru_gate_kernel(const float* __restrict__ u32, const float* __restrict__ gates, const float* __restrict__ y_logit,
@@ -280,10 +279,9 @@ __global__ void rglru_gate_kernel(const float* __restrict__ u32, const float* __
                                   int blocks) {
     pdl_launch_dependents();
     pdl_wait();      // everything this kernel reads may come from the kernel before
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long n = (long long)tokens * width;
-    if (i >= n) return;
-    const int t = (int)(i / width), c = (int)(i % width);
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;       // a token per block row: no division per element
+    if (c >= width) return;
+    const size_t n = (size_t)tokens * width, i = (size_t)t * width + c;
     const int bw = width / blocks, b = c / bw, cb = c % bw;
     const float* g = gates + ((size_t)b * tokens + t) * 2 * bw + cb;
     const float rg = sigmoidf_(g[0]), ig = sigmoidf_(g[bw]);
@@ -413,7 +411,7 @@ NIB_API int nib_rglru_scan(const float* u32, const float* gates, const float* y_
                                 ldx, softplus_lam, state, q_start, slots, (__nv_bfloat16*)out, tokens, width, taps, blocks));
         return 0;
     }
-    NIB_CUDA(launch_pdl(rglru_gate_kernel, dim3(ceil_div((long long)tokens * width, 256)), dim3(256), (size_t)(0), stream, u32, gates, y_logit, ldy, softplus_lam, work,
+    NIB_CUDA(launch_pdl(rglru_gate_kernel, dim3(tokens, ceil_div(width, 256)), dim3(256), (size_t)(0), stream, u32, gates, y_logit, ldy, softplus_lam, work,
                                                                                     tokens, width, blocks));
     NIB_LAUNCH_CHECK();
     const dim3 grid(ceil_div(width, 32), requests);
