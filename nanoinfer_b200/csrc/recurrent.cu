@@ -44,7 +44,8 @@ delta_rule_prepare_kernel(const float* __restrict__ k, const float* __restrict__
     const float inv = 1.0f / sqrtf(ss + 1e-6f);
     for (int ch = lane; ch < d; ch += 32) {
         const float u = k[in + ch] * inv;
-        work[out + ch] = expf(-0.60653065971263342f * sigmoidf_(w_logit[inw + ch]));      // exp(-exp(-1/2) sigmoid)
+        // exp(-exp(-1/2) sigmoid), rounded to 32 bits once from a 64-bit exponential (see rglru_gate_kernel)
+        work[out + ch] = (float)exp(-0.60653065971263342 * (double)sigmoidf_(w_logit[inw + ch]));
         work[plane + out + ch] = u;
         work[2 * plane + out + ch] = sigmoidf_(a_logit[in + ch]) * u;
     }
@@ -286,8 +287,11 @@ __global__ void rglru_gate_kernel(const float* __restrict__ u32, const float* __
     const float* g = gates + ((size_t)b * tokens + t) * 2 * bw + cb;
     const float rg = sigmoidf_(g[0]), ig = sigmoidf_(g[bw]);
     const float log_a = -8.0f * rg * softplus_lam[c];
-    work[i] = expf(log_a);
-    work[n + i] = sqrtf(fmaxf(0.f, -expm1f(2.0f * log_a))) * (ig * u32[i]);      // sqrt(1 - a^2) (i u)
+    // The decay is raised to hundreds of powers along a sequence: it is rounded to 32 bits once, from a 64-bit
+    // exponential (expf alone may be two units in the last place off, which a long memory multiplies up).
+    const double la = (double)log_a;
+    work[i] = (float)exp(la);
+    work[n + i] = (float)sqrt(fmax(0.0, -expm1(2.0 * la))) * (ig * u32[i]);      // sqrt(1 - a^2) (i u)
     const float z = y_logit[(size_t)t * ldy + c];
     work[2 * n + i] = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
@@ -379,8 +383,8 @@ rglru_few_tokens_kernel(const float* __restrict__ u32, const float* __restrict__
     for (int t = 0; t < n; ++t) {
         const size_t row = (size_t)(t0 + t);
         const float rg = sigmoidf_(g[row * 2 * bw]), ig = sigmoidf_(g[row * 2 * bw + bw]);
-        const float log_a = -8.0f * rg * sp;
-        S = fmaf(expf(log_a), S, sqrtf(fmaxf(0.f, -expm1f(2.0f * log_a))) * (ig * u32[row * width + c]));
+        const double la = (double)(-8.0f * rg * sp);        // as in rglru_gate_kernel
+        S = fmaf((float)exp(la), S, (float)sqrt(fmax(0.0, -expm1(2.0 * la))) * (ig * u32[row * width + c]));
         const float z = y_logit[row * ldy + c];
         Elem<T>::store(out + row * width + c, S * (0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)))));
     }
