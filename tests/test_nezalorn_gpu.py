@@ -243,6 +243,28 @@ def test_conv_and_recurrence_in_steps(ops, dtype, width, taps, blocks):
         assert_close(state, ref_state, torch.float32, f"state step {i}")
 
 
+def test_a_slow_decay_keeps_its_accuracy_over_thousands_of_tokens(ops):
+    """Decays within a thousandth of one, 3,000 tokens: the state must stay within 2e-6 of a 64-bit recurrence. (With the
+    decay from a 32-bit exponential, which may be two units in the last place off, it drifts to about 9e-6.)"""
+    width, m = 64, 3000
+    g = torch.Generator().manual_seed(0)
+    gates = torch.empty(1, m, 2 * width)
+    gates[..., :width] = -5.0 + 0.5 * torch.randn(m, width, generator=g)       # the recurrence gate near 0.007
+    gates[..., width:] = 3.0
+    sp = torch.full((width,), 0.02)                                             # log a near -1e-3
+    u, y = torch.randn(m, width, generator=g), torch.randn(m, width, generator=g)
+    ctx, _, _ = batch([m], [0])
+    state, out = torch.zeros(1, 1, width, device=DEV), torch.empty(m, width, device=DEV)
+    ops.rglru_scan(u.to(DEV), gates.to(DEV), y.to(DEV), u.to(DEV), sp.to(DEV), state, ctx, out, 1, 1)
+    la = -8.0 * torch.sigmoid(gates[0, :, :width].double()) * sp.double()
+    a, b = torch.exp(la), torch.sqrt(-torch.expm1(2 * la)) * torch.sigmoid(gates[0, :, width:].double()) * u.double()
+    ref = torch.zeros(width, dtype=torch.float64)
+    for t in range(m):
+        ref = a[t] * ref + b[t]
+    err = ((state[0, 0].double().cpu() - ref).abs().max() / ref.abs().max()).item()
+    assert err < 2e-6, err
+
+
 # ------------------------------------------------------------------------------------------ attention through a latent
 def _freq(rot):
     from nanoinfer_b200.parts.position import scaled_frequencies
