@@ -2,6 +2,7 @@
 from . import spec, base  # noqa: F401
 from . import norm, position, attention, feedforward, embedding, block  # noqa: F401
 from . import latent_attention, delta_rule, rglru, depth  # noqa: F401
+from . import flex_attention, linear_state, side_by_side  # noqa: F401
 from .spec import ModelPlan, LayerSpec, PartSpec, ScheduleEntry, TensorSpec
 from .base import (CacheNeed, PagedTensor, FoldedNorm, LazyNorm, StateNeed, StepContext, HostBatch, LayerCache, Runtime, Part, Norm,
                    PositionEncoding, Mixer, FeedForward, Embedding, Head)

@@ -34,7 +34,8 @@ class PreNormBlock:
 
 class ParallelBlock:
     """``x <- x + mixer(norm_a(x)) + feed_forward(norm_b(x))``: both branches read the same x. parts: ``mixer_norm``,
-    ``mixer``; optionally ``ffn_norm`` and ``ffn`` (a layer without a feed-forward), and ``depth`` (a part with
+    ``mixer``; optionally ``ffn`` (a layer without a feed-forward) with ``ffn_norm`` (without it the feed-forward reads
+    the mixer's norm: one norm for both branches), and ``depth`` (a part with
     ``begin(x32, ctx)`` before and ``forward(x32, ctx)`` after the layer: what goes on is a mix of this and earlier
     results). Both norms are computed before either branch adds to the stream."""
 
@@ -44,11 +45,12 @@ class ParallelBlock:
         self.mixer_norm, self.mixer = parts["mixer_norm"], parts["mixer"]
         self.ffn_norm, self.ffn = parts.get("ffn_norm"), parts.get("ffn")
         self.depth = parts.get("depth")
-        if (self.ffn is None) != (self.ffn_norm is None):
-            raise ValueError("a parallel block has a feed-forward and its norm, or neither")
+        if self.ffn is None and self.ffn_norm is not None:
+            raise ValueError("a parallel block without a feed-forward has no norm for one")
         self.part_names = tuple(n for n in ("mixer_norm", "mixer", "ffn_norm", "ffn", "depth") if parts.get(n) is not None)
 
     def forward(self, x32: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
+        shared = self.ffn is not None and self.ffn_norm is None      # both branches read the mixer's norm
         together = getattr(self.mixer_norm, "forward_with", None) if type(self.mixer_norm) is type(self.ffn_norm) else None
         pending = ctx.scratch.pop(PENDING_STREAM_OP, None)      # what the layer before left to do on the stream
         fused = pending is not None and together is not None and hasattr(pending, "run_with_norms") \
@@ -61,7 +63,7 @@ class ParallelBlock:
             h_mixer, h_ffn = together(self.ffn_norm, x32)
         else:
             h_mixer = self.mixer_norm.forward(x32)
-            h_ffn = self.ffn_norm.forward(x32) if self.ffn is not None else None
+            h_ffn = h_mixer if shared else (self.ffn_norm.forward(x32) if self.ffn is not None else None)
         if self.depth is not None:
             self.depth.begin(x32, ctx)
         self.mixer.forward(h_mixer, x32, ctx, cache)

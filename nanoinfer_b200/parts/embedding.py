@@ -15,23 +15,30 @@ from .spec import PartSpec, TensorSpec
 
 
 class TokenEmbedding(Embedding):
-    """params: ``vocab``, ``hidden``. tensors: ``table [vocab, hidden]``."""
+    """params: ``vocab``, ``hidden``, optionally ``scale`` (a factor on every row, applied in 32-bit).
+    tensors: ``table [vocab, hidden]``."""
 
     graph_safe = True   # launches do not depend on which requests are in the batch
 
     @staticmethod
-    def spec(name: str, vocab: int, hidden: int) -> PartSpec:
-        return PartSpec("token_embedding", {"vocab": vocab, "hidden": hidden},
-                        {"table": TensorSpec(name, (vocab, hidden), "embedding")})
+    def spec(name: str, vocab: int, hidden: int, scale: float = 1.0) -> PartSpec:
+        params = {"vocab": vocab, "hidden": hidden}
+        if scale != 1.0:
+            params["scale"] = float(scale)
+        return PartSpec("token_embedding", params, {"table": TensorSpec(name, (vocab, hidden), "embedding")})
 
     def __init__(self, spec: PartSpec, tensors: Dict[str, torch.Tensor], rt: Runtime):
         super().__init__(spec, tensors, rt)
         self.vocab, self.hidden = int(spec.params["vocab"]), int(spec.params["hidden"])
         self.table = rt.matrix(tensors["table"])
+        self.scale = float(spec.params.get("scale", 1.0))
 
     def forward(self, token_ids: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         x32 = torch.empty((token_ids.shape[0], self.hidden), dtype=torch.float32, device=token_ids.device)
-        self.ops.embed(token_ids, self.table, x32)
+        if self.scale == 1.0:
+            self.ops.embed(token_ids, self.table, x32)
+        else:
+            self.ops.embed(token_ids, self.table, x32, self.scale)
         return x32
 
 

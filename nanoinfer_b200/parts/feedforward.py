@@ -22,11 +22,13 @@ class SwiGLU(FeedForward):
     accepts_lazy_norm = True   # its first projection can apply the norm while reading its input
 
     @staticmethod
-    def spec(prefix: str, hidden: int, intermediate: int) -> PartSpec:
+    def spec(prefix: str, hidden: int, intermediate: int,
+             names=("gate_proj.weight", "up_proj.weight", "down_proj.weight")) -> PartSpec:
+        """``names``: what the gate, up and down matrices are called behind ``prefix``."""
         return PartSpec("swiglu", {"hidden": hidden, "intermediate": intermediate}, {
-            "gate_w": TensorSpec(f"{prefix}.gate_proj.weight", (intermediate, hidden)),
-            "up_w": TensorSpec(f"{prefix}.up_proj.weight", (intermediate, hidden)),
-            "down_w": TensorSpec(f"{prefix}.down_proj.weight", (hidden, intermediate)),
+            "gate_w": TensorSpec(f"{prefix}.{names[0]}", (intermediate, hidden)),
+            "up_w": TensorSpec(f"{prefix}.{names[1]}", (intermediate, hidden)),
+            "down_w": TensorSpec(f"{prefix}.{names[2]}", (hidden, intermediate)),
         })
 
     def __init__(self, spec: PartSpec, tensors: Dict[str, torch.Tensor], rt: Runtime):

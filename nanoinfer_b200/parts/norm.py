@@ -15,20 +15,24 @@ from .spec import PartSpec, TensorSpec
 
 
 class RMSNorm(Norm):
-    """params: ``size`` (width of a row), ``eps``. tensors: ``gain [size]``."""
+    """params: ``size`` (width of a row), ``eps``, optionally ``gain_offset`` (a gain stored around zero: the row is
+    multiplied by ``gain_offset + gain``, summed once in 32-bit when the weights are loaded). tensors: ``gain [size]``."""
 
     graph_safe = True   # launches do not depend on which requests are in the batch
 
     @staticmethod
-    def spec(size: int, eps: float, gain_name: str) -> PartSpec:
-        return PartSpec("rmsnorm", {"size": size, "eps": eps},
-                        {"gain": TensorSpec(gain_name, (size,), "gain")})
+    def spec(size: int, eps: float, gain_name: str, gain_offset: float = 0.0) -> PartSpec:
+        params = {"size": size, "eps": eps}
+        if gain_offset:
+            params["gain_offset"] = float(gain_offset)
+        return PartSpec("rmsnorm", params, {"gain": TensorSpec(gain_name, (size,), "bias" if gain_offset else "gain")})
 
     def __init__(self, spec: PartSpec, tensors: Dict[str, torch.Tensor], rt: Runtime):
         super().__init__(spec, tensors, rt)
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
-        self.gain = rt.vector32(tensors["gain"])
+        offset = float(spec.params.get("gain_offset", 0.0))
+        self.gain = rt.vector32(tensors["gain"].to(torch.float32) + offset if offset else tensors["gain"])
 
     def forward(self, x32: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = x32.shape[0] if rows is None else rows.shape[0]

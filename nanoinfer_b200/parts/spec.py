@@ -18,7 +18,7 @@ class TensorSpec:
     """One checkpoint tensor that a part needs."""
     name: str                 # tensor name in the safetensors file
     shape: Tuple[int, ...]
-    init: str = "matrix"      # random-weights rule: "matrix" | "gain" | "bias" | "embedding" | "unit" | "mix"
+    init: str = "matrix"      # random-weights rule: "matrix" | "gain" | "bias" | "embedding" | "unit" | "mix" | "mix01"
     integer: bool = False     # an integer table (kept as int32); everything else must be stored as floats
 
 

@@ -35,6 +35,8 @@ def random_tensor(ts: TensorSpec, seed: int, dtype: torch.dtype) -> torch.Tensor
         x = 1.0 + 0.1 * x
     elif ts.init == "mix":      # weights of an average: each near 1/n
         x = (1.0 + 0.3 * x) / max(1, x.numel())
+    elif ts.init == "mix01":    # blend factors between two inputs: uniform in 0..1
+        x = torch.rand(ts.shape, generator=g, dtype=torch.float32)
     elif ts.init in _STD:
         x = _STD[ts.init] * x
     else:

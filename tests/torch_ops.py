@@ -14,8 +14,8 @@ from nanoinfer_b200.parts.base import as_tensor
 class TorchOps:
     name = "torch-reference"
 
-    def embed(self, ids, table, out32):
-        out32.copy_(table[ids.long()].to(torch.float32))
+    def embed(self, ids, table, out32, scale=1.0):
+        out32.copy_((table[ids.long()].double() * scale).to(torch.float32))
 
     def rmsnorm(self, x32, gain32, eps, out, rows=None):
         x = x32.double() if rows is None else x32[rows.long()].double()
@@ -131,6 +131,163 @@ class TorchOps:
         if bias32 is not None:
             y = y + bias32.double()[:, None, :]
         out32.copy_(y.to(torch.float32))
+
+    # ---- attention with options (attention_flex.cu) --------------------------------------------------
+    def attention_prepare(self, qkv32, q_out, heads, kv_heads, dim, vdim, q_gain32, k_gain32, eps, freq32, rot_dims, ctx,
+                          block_table, page_size, k_pages, v_pages, writes):
+        m = qkv32.shape[0]
+        nq, nk = heads * dim, kv_heads * dim
+        q = qkv32[:, :nq].double().reshape(m, heads, dim)
+        k = qkv32[:, nq:nq + nk].double().reshape(m, kv_heads, dim)
+        v = qkv32[:, nq + nk:].double().reshape(m, kv_heads, vdim)
+        if q_gain32 is not None:
+            q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_gain32.double()
+            k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_gain32.double()
+        if rot_dims:
+            half = rot_dims // 2
+            ang = ctx.positions.double()[:, None] * freq32.double()[None, :]
+            c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+            def turn(x):
+                a, b = x[..., :half].clone(), x[..., half:rot_dims].clone()
+                x = x.clone()
+                x[..., :half] = a * c - b * s
+                x[..., half:rot_dims] = b * c + a * s
+                return x
+            q, k = turn(q), turn(k)
+        q_out.copy_(q.reshape(m, nq).to(q_out.dtype))
+        if not writes:
+            return
+        pos = ctx.positions.long()
+        page = block_table[ctx.req_index.long(), pos // page_size].long()
+        ok = page >= 0      # padding rows of a replayed step hold no pages
+        k_pages[page[ok], :, (pos % page_size)[ok], :] = k[ok].to(k_pages.dtype)
+        v_pages[page[ok], :, (pos % page_size)[ok], :] = v[ok].to(v_pages.dtype)
+
+    def attention_flex(self, q, out, heads, kv_heads, dim, vdim, scale, softcap, slopes32, window, chunk, out_scale, ctx,
+                       block_table, page_size, k_pages, v_pages):
+        m = q.shape[0]
+        qh = q.double().view(m, heads, dim)
+        rep = heads // kv_heads
+        res = torch.zeros(m, heads, vdim, dtype=torch.float64, device=q.device)
+        for t in range(m):
+            pos, r = int(ctx.positions[t]), int(ctx.req_index[t])
+            lo = max(0, pos - window + 1) if window else 0
+            if chunk:
+                lo = max(lo, (pos // chunk) * chunk)
+            js = torch.arange(lo, pos + 1)
+            pages = block_table[r, js // page_size].long()
+            if (pages < 0).any():
+                continue        # a padding row
+            k = k_pages[pages, :, js % page_size, :].double()       # [keys, kv_heads, dim]
+            v = v_pages[pages, :, js % page_size, :].double()
+            for h in range(heads):
+                s = (k[:, h // rep] @ qh[t, h]) * scale
+                if softcap:
+                    s = softcap * torch.tanh(s / softcap)
+                if slopes32 is not None:
+                    s = s - slopes32[h].double() * (pos - js).double()
+                res[t, h] = torch.softmax(s, 0) @ v[:, h // rep]
+        out.copy_((res.view(m, heads * vdim) * out_scale).to(out.dtype))
+
+    # ---- gate, norm in groups, skip (pointwise.cu) ---------------------------------------------------
+    def gated_norm(self, o32, out, groups=0, eps=0.0, gain32=None, gate32=None, gate_kind="none", gate_first=False,
+                   skip32=None, skip_coef32=None, out_scale=1.0):
+        m, n = o32.shape
+        y = o32.double()
+        if skip32 is not None:
+            y = y + skip32.double() * skip_coef32.double().repeat_interleave(n // skip_coef32.numel())
+        act = {"sigmoid": torch.sigmoid, "silu": lambda z: z * torch.sigmoid(z)}.get(gate_kind)
+        if act is not None and gate_first:
+            y = y * act(gate32.double())
+        if groups:
+            y = y.view(m, groups, n // groups)
+            y = (y / torch.sqrt(y.pow(2).mean(-1, keepdim=True) + eps)).reshape(m, n)
+        if gain32 is not None:
+            y = y * gain32.double().repeat(n // gain32.numel())
+        if act is not None and not gate_first:
+            y = y * act(gate32.double())
+        out.copy_((y * out_scale).to(out.dtype))
+
+    # ---- matrix states that decay (linear_state.cu) --------------------------------------------------
+    def conv_tokens(self, x32, w32, bias32, act, state, state_off, ctx, out32, taps):
+        start = 0
+        width = x32.shape[1]
+        for q_len, slot in zip(ctx.host.q_lens, ctx.host.slots):
+            if taps > 1:
+                hist = state[slot, state_off:state_off + (taps - 1) * width].double().view(taps - 1, width)
+            else:
+                hist = torch.zeros(0, width, dtype=torch.float64)
+            padded = torch.cat([hist, x32[start:start + q_len].double()], 0)
+            u = torch.zeros(q_len, width, dtype=torch.float64)
+            for j in range(taps):
+                u += padded[j:j + q_len] * w32[:, j].double()
+            if bias32 is not None:
+                u = u + bias32.double()
+            if act == "silu":
+                u = u * torch.sigmoid(u)
+            out32[start:start + q_len] = u.to(torch.float32)
+            start += q_len
+
+    def conv_tail(self, x32, state, state_off, ctx, taps):
+        start = 0
+        width = x32.shape[1]
+        for q_len, slot in zip(ctx.host.q_lens, ctx.host.slots):
+            hist = state[slot, state_off:state_off + (taps - 1) * width].view(taps - 1, width)
+            padded = torch.cat([hist.clone(), x32[start:start + q_len]], 0)
+            hist.copy_(padded[-(taps - 1):])
+            start += q_len
+
+    def token_shift(self, h, mu32, state, state_off, ctx, mixes):
+        start = 0
+        width = h.shape[1]
+        for q_len, slot in zip(ctx.host.q_lens, ctx.host.slots):
+            cur = h[start:start + q_len].double()
+            prev = torch.cat([state[slot, state_off:state_off + width].double()[None, :], cur[:-1]], 0)
+            for s in range(mu32.shape[0]):
+                mixes[s, start:start + q_len] = (cur + (prev - cur) * mu32[s].double()).to(mixes.dtype)
+            state[slot, state_off:state_off + width] = cur[-1].to(torch.float32)
+            start += q_len
+
+    def decay_map(self, z32, out32, kind, param):
+        z = z32.double()
+        if kind == "sigmoid_root":
+            out32.copy_(torch.exp(torch.nn.functional.logsigmoid(z) / param).to(torch.float32))
+        elif kind == "exp_neg_exp":
+            out32.copy_(torch.exp(-torch.exp(z)).to(torch.float32))
+        else:
+            raise ValueError(kind)
+
+    def step_sizes(self, dt_raw32, dt_bias32, a_log32, dt_out, decay_out):
+        dt = torch.nn.functional.softplus(dt_raw32.double() + dt_bias32.double(), threshold=1e9)
+        dt_out.copy_(dt.to(torch.float32))
+        decay_out.copy_(torch.exp(-torch.exp(a_log32.double()) * dt_out.double()).to(torch.float32))
+
+    def linear_state_scan(self, q32, k32, v32, w32, state, state_off, ctx, o32, heads, kq_heads, dk, dv, q_scale=1.0,
+                          bonus32=None, v_scale32=None):
+        start = 0
+        rep = heads // kq_heads
+        per_channel = w32.shape[1] == heads * dk
+        for q_len, slot in zip(ctx.host.q_lens, ctx.host.slots):
+            flat = state[slot, state_off:state_off + heads * dv * dk]
+            s = flat.double().view(heads, dv, dk).transpose(1, 2).clone()      # [head, key channel, value channel]
+            for t in range(start, start + q_len):
+                q = (q32[t].double() * q_scale).view(kq_heads, dk).repeat_interleave(rep, 0)
+                k = k32[t].double().view(kq_heads, dk).repeat_interleave(rep, 0)
+                v = v32[t].double().view(heads, dv)
+                if v_scale32 is not None:
+                    v = v * v_scale32[t].double()[:, None]
+                w = w32[t].double().view(heads, dk) if per_channel else w32[t].double()[:, None].expand(heads, dk)
+                kv = k[:, :, None] * v[:, None, :]
+                if bonus32 is not None:
+                    o = torch.einsum("hkv,hk->hv", s + bonus32.double()[:, :, None] * kv, q)
+                    s = w[:, :, None] * s + kv
+                else:
+                    s = w[:, :, None] * s + kv
+                    o = torch.einsum("hkv,hk->hv", s, q)
+                o32[t] = o.reshape(-1).to(torch.float32)
+            flat.copy_(s.transpose(1, 2).reshape(-1).to(torch.float32))
+            start += q_len
 
     # ---- recurrent mixers of recurrent.cu -----------------------------------------------------------
     def delta_rule_scan(self, r32, k32, v32, a_logit32, w_logit32, state, ctx, o32, heads, d):
