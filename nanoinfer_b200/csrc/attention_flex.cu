@@ -1,0 +1,223 @@
+// Softmax attention over the paged cache with the options that decoder designs combine, and the kernel that prepares
+// its operands. All arithmetic is 32-bit whatever the storage type T (float or bfloat16).
+//
+//  * attention_prepare: from the 32-bit rows [q | k | v] of a step (after projection, bias and any convolution): every q
+//    and k head optionally divided by its root mean square and multiplied by a gain of the head's size (shared by the
+//    heads), the first `rot` elements of every q and k head turned by angle = position * freq[i] (element i paired with
+//    i + rot/2; the angle is formed in 32-bit), queries written in the storage type, keys and values written into their
+//    pages. Keys are `dk` wide, values `dv`. One warp per (token, head of q, k or v).
+//  * attention_flex: one warp per (token, query head). A query at position p of its request sees the keys j <= p,
+//    with a window only j > p - window, with a chunk only floor(j / chunk) == floor(p / chunk) (counted from the
+//    request's position 0). score = (q . k) * scale; with a cap c: c tanh(score / c); with slopes: minus
+//    slope[head] * (p - j). Keys are taken in blocks of 32 that start at absolute multiples of 32 with a running
+//    maximum and sum, so a position's result does not depend on how the request was cut into steps, nor on what else
+//    is in the batch. The output (dv wide per head) is multiplied by out_scale and written as float or T.
+#include "common.cuh"
+
+constexpr int FX_MAX_D = 256;
+constexpr int FX_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(FX_WARPS * 32)
+attention_prepare_kernel(const float* __restrict__ qkv, int ld, T* __restrict__ q_out, const float* __restrict__ q_gain,
+                         const float* __restrict__ k_gain, float eps, const float* __restrict__ freq, int rot,
+                         const int* __restrict__ positions, const int* __restrict__ req_index, const int* __restrict__ block_table,
+                         int bt_stride, int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages,
+                         int tokens, int heads, int kv_heads, int dk, int dv, int writes) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    __shared__ float x_s[FX_WARPS][FX_MAX_D];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_token = heads + 2 * kv_heads;
+    const long long wid = (long long)blockIdx.x * FX_WARPS + warp;
+    if (wid >= (long long)tokens * per_token) return;
+    const int t = (int)(wid / per_token), s = (int)(wid % per_token);
+    const int pos = positions[t];
+    const bool is_q = s < heads, is_k = !is_q && s < heads + kv_heads;
+    const int head = is_q ? s : (is_k ? s - heads : s - heads - kv_heads);
+    const int d = (is_q || is_k) ? dk : dv;
+    const float* src = qkv + (size_t)t * ld + (is_q ? (size_t)head * dk : (is_k ? (size_t)heads * dk + (size_t)head * dk
+                                                                                   : (size_t)(heads + kv_heads) * dk + (size_t)head * dv));
+    T* dst = nullptr;
+    if (is_q) {
+        dst = q_out + (size_t)t * heads * dk + (size_t)head * dk;
+    } else if (writes) {
+        const int page = block_table[(size_t)req_index[t] * bt_stride + pos / page_size];
+        if (page >= 0 && page < num_pages)      // a padding row of a replayed step holds no pages
+            dst = (is_k ? k_pages : v_pages) + (((size_t)page * kv_heads + head) * page_size + (pos % page_size)) * d;
+    }
+    if (dst == nullptr) return;
+    if (!is_q && !is_k) {
+        for (int c = lane; c < d; c += 32) Elem<T>::store(dst + c, src[c]);
+        return;
+    }
+    const float* gain = is_q ? q_gain : k_gain;
+    float norm = 1.0f;
+    if (gain != nullptr) {
+        float ss = 0.f;
+        for (int c = lane; c < d; c += 32) ss = fmaf(src[c], src[c], ss);
+        norm = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
+    }
+    for (int c = lane; c < d; c += 32) x_s[warp][c] = gain != nullptr ? src[c] * norm * gain[c] : src[c];
+    __syncwarp();
+    const int half = rot >> 1;
+    for (int c = lane; c < d; c += 32) {
+        float y = x_s[warp][c];
+        if (c < rot) {
+            const int i = c < half ? c : c - half;
+            const float a = (float)pos * freq[i];
+            const float cs = cosf(a), sn = sinf(a);
+            y = c < half ? y * cs - x_s[warp][c + half] * sn : y * cs + x_s[warp][c - half] * sn;
+        }
+        Elem<T>::store(dst + c, y);
+    }
+}
+
+NIB_API int nib_attention_prepare(const float* qkv, int ld, void* q_out, const float* q_gain, const float* k_gain, float eps,
+                                  const float* freq, int rot, const int* positions, const int* req_index, const int* block_table,
+                                  int bt_stride, int page_size, void* k_pages, void* v_pages, int num_pages, int tokens, int heads,
+                                  int kv_heads, int dk, int dv, int writes, int dtype, cudaStream_t stream) {
+    NIB_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0, "attention_prepare: bad head counts");
+    NIB_REQUIRE(dk > 0 && dk <= FX_MAX_D && dv > 0 && dv <= FX_MAX_D, "attention_prepare: head sizes %d / %d are outside 1..%d", dk, dv, FX_MAX_D);
+    NIB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dk && (rot == 0 || freq != nullptr), "attention_prepare: bad rotated width %d", rot);
+    NIB_REQUIRE((q_gain == nullptr) == (k_gain == nullptr), "attention_prepare: q and k are normed together or not at all");
+    NIB_REQUIRE(!writes || (page_size > 0 && num_pages > 0 && block_table != nullptr), "attention_prepare: bad pages");
+    if (tokens == 0) return 0;
+    const dim3 grid(ceil_div((long long)tokens * (heads + 2 * kv_heads), FX_WARPS)), block(FX_WARPS * 32);
+    if (dtype == NIB_F32)
+        NIB_CUDA(launch_pdl(attention_prepare_kernel<float>, grid, block, (size_t)0, stream, qkv, ld, (float*)q_out, q_gain, k_gain, eps, freq, rot,
+                            positions, req_index, block_table, bt_stride, page_size, (float*)k_pages, (float*)v_pages, num_pages, tokens, heads,
+                            kv_heads, dk, dv, writes));
+    else if (dtype == NIB_BF16)
+        NIB_CUDA(launch_pdl(attention_prepare_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, qkv, ld, (__nv_bfloat16*)q_out, q_gain, k_gain,
+                            eps, freq, rot, positions, req_index, block_table, bt_stride, page_size, (__nv_bfloat16*)k_pages,
+                            (__nv_bfloat16*)v_pages, num_pages, tokens, heads, kv_heads, dk, dv, writes));
+    else
+        NIB_REQUIRE(false, "attention_prepare: unknown dtype %d", dtype);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+__device__ __forceinline__ float dot_row(const float* __restrict__ q_s, const T* __restrict__ kr, int dk) {
+    float dot = 0.f;
+    for (int d = 0; d < dk; ++d) dot = fmaf(q_s[d], Elem<T>::load(kr + d), dot);
+    return dot;
+}
+
+// bfloat16 rows of a multiple of 8 elements are read 16 bytes at a time (rows then start on 16-byte boundaries)
+template <>
+__device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* __restrict__ q_s, const __nv_bfloat16* __restrict__ kr, int dk) {
+    float dot = 0.f;
+    if ((dk & 7) == 0) {
+        const uint4* k4 = reinterpret_cast<const uint4*>(kr);
+        for (int d8 = 0; d8 < dk / 8; ++d8) {
+            const uint4 raw = k4[d8];
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(p[i]);
+                dot = fmaf(q_s[d8 * 8 + 2 * i], f.x, dot);
+                dot = fmaf(q_s[d8 * 8 + 2 * i + 1], f.y, dot);
+            }
+        }
+        return dot;
+    }
+    for (int d = 0; d < dk; ++d) dot = fmaf(q_s[d], __bfloat162float(kr[d]), dot);
+    return dot;
+}
+
+template <typename T, typename TO>
+__global__ void __launch_bounds__(FX_WARPS * 32)
+attention_flex_kernel(const T* __restrict__ q, int q_stride, TO* __restrict__ out, const int* __restrict__ positions,
+                      const int* __restrict__ req_index, const int* __restrict__ block_table, int bt_stride, int page_size,
+                      const T* __restrict__ k_pages, const T* __restrict__ v_pages, int num_pages, int m_tokens, int heads,
+                      int kv_heads, int dk, int dv, float scale, float softcap, const float* __restrict__ slopes, int window,
+                      int chunk, float out_scale) {
+    __shared__ __align__(16) float q_s[FX_WARPS][FX_MAX_D];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long w = (long long)blockIdx.x * FX_WARPS + warp;
+    if (w >= (long long)m_tokens * heads) return;
+    const int token = (int)(w / heads), head = (int)(w % heads);
+    const int kvh = head / (heads / kv_heads);
+    const int pos = positions[token];
+    const int* bt = block_table + (size_t)req_index[token] * bt_stride;
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
+    const float slope = slopes != nullptr ? slopes[head] : 0.f;
+    const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
+
+    const T* qr = q + (size_t)token * q_stride + (size_t)head * dk;
+    for (int d = lane; d < dk; d += 32) q_s[warp][d] = Elem<T>::load(qr + d);
+    __syncwarp();
+
+    float m_run = -INFINITY, l_run = 0.f;
+    float acc[FX_MAX_D / 32];
+#pragma unroll
+    for (int i = 0; i < FX_MAX_D / 32; ++i) acc[i] = 0.f;
+
+    for (int kb = (lo / 32) * 32; kb <= pos; kb += 32) {
+        const int j = kb + lane;
+        const bool valid = (j >= lo) && (j <= pos);
+        float s = -INFINITY;
+        long long slot = -1;  // row of this lane's key in the pages: (page * kv_heads + kvh) * page_size + offset
+        if (valid) {
+            const int page = bt[j / page_size];
+            if (page >= 0 && page < num_pages) {
+                slot = ((long long)page * kv_heads + kvh) * page_size + (j % page_size);
+                s = dot_row<T>(q_s[warp], k_pages + slot * dk, dk) * scale;
+                if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
+                s -= slope * (float)(pos - j);
+            }
+        }
+        const float m_new = fmaxf(m_run, warp_max(s));
+        const float p = (s == -INFINITY) ? 0.f : expf(s - m_new);
+        const float corr = (m_run == -INFINITY) ? 0.f : expf(m_run - m_new);
+        l_run = l_run * corr + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < FX_MAX_D / 32; ++i) acc[i] *= corr;
+        for (int jj = 0; jj < 32; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const long long rj = __shfl_sync(0xffffffffu, slot, jj);
+            if (pj == 0.f || rj < 0) continue;  // uniform over the warp
+            const T* vr = v_pages + rj * dv;
+#pragma unroll
+            for (int i = 0; i < FX_MAX_D / 32; ++i) {
+                const int d = lane + 32 * i;
+                if (d < dv) acc[i] = fmaf(pj, Elem<T>::load(vr + d), acc[i]);
+            }
+        }
+        m_run = m_new;
+    }
+    TO* o = out + (size_t)token * heads * dv + (size_t)head * dv;
+    const float inv = l_run > 0.f ? out_scale / l_run : 0.f;
+#pragma unroll
+    for (int i = 0; i < FX_MAX_D / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < dv) Elem<TO>::store(o + d, acc[i] * inv);
+    }
+}
+
+// q: rows of q_stride elements whose first heads*dk are the prepared queries. out: [m_tokens, heads*dv], float when
+// out_f32, else T. Pages: k [num_pages, kv_heads, page_size, dk], v [num_pages, kv_heads, page_size, dv].
+NIB_API int nib_attention_flex(const void* q, int q_stride, void* out, int out_f32, const int* positions, const int* req_index,
+                               const int* block_table, int bt_stride, int page_size, const void* k_pages, const void* v_pages,
+                               int num_pages, int m_tokens, int heads, int kv_heads, int dk, int dv, float scale, float softcap,
+                               const float* slopes, int window, int chunk, float out_scale, int dtype, cudaStream_t stream) {
+    NIB_REQUIRE(m_tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "attention: bad head counts %d / %d", heads, kv_heads);
+    NIB_REQUIRE(dk > 0 && dk <= FX_MAX_D && dv > 0 && dv <= FX_MAX_D, "attention: head sizes %d / %d are outside 1..%d", dk, dv, FX_MAX_D);
+    NIB_REQUIRE(page_size > 0 && num_pages > 0 && window >= 0 && chunk >= 0 && softcap >= 0.f, "attention: bad page_size/num_pages/window/chunk/cap");
+    if (m_tokens == 0) return 0;
+    const int blocks = ceil_div((long long)m_tokens * heads, FX_WARPS);
+#define NIB_FX_LAUNCH(T, TO)                                                                                                       \
+    attention_flex_kernel<T, TO><<<blocks, FX_WARPS * 32, 0, stream>>>((const T*)q, q_stride, (TO*)out, positions, req_index, block_table, \
+        bt_stride, page_size, (const T*)k_pages, (const T*)v_pages, num_pages, m_tokens, heads, kv_heads, dk, dv, scale, softcap, slopes,  \
+        window, chunk, out_scale)
+    if (dtype == NIB_F32) NIB_FX_LAUNCH(float, float);
+    else if (dtype == NIB_BF16 && out_f32) NIB_FX_LAUNCH(__nv_bfloat16, float);
+    else if (dtype == NIB_BF16) NIB_FX_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else NIB_REQUIRE(false, "attention: unknown dtype %d", dtype);
+#undef NIB_FX_LAUNCH
+    NIB_LAUNCH_CHECK();
+    return 0;
+}

@@ -11,7 +11,7 @@
 // ---------------------------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                             float* __restrict__ out, int hidden, int vocab, unsigned long long* trace, int trace_cap) {
+                             float* __restrict__ out, int hidden, int vocab, float scale, unsigned long long* trace, int trace_cap) {
     const int m = blockIdx.x;
     if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_EMBED, 0, 1);
     const int id = ids[m];
@@ -21,23 +21,29 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
         return;
     }
     const T* src = table + (size_t)id * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = Elem<T>::load(src + c);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = Elem<T>::load(src + c) * scale;
     if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_EMBED, 0, 2);
 }
 
-NIB_API int nib_embed(const int* ids, const void* table, float* out, int m, int hidden, int vocab,
-                      int dtype, cudaStream_t stream) {
+// Rows of the table times ``scale`` (1 for a plain gather), in 32-bit.
+NIB_API int nib_embed_scaled(const int* ids, const void* table, float* out, int m, int hidden, int vocab,
+                             int dtype, float scale, cudaStream_t stream) {
     NIB_REQUIRE(m >= 0 && hidden > 0 && vocab > 0, "embed: bad sizes m=%d hidden=%d vocab=%d", m, hidden, vocab);
     if (m == 0) return 0;
     const int threads = hidden >= 256 ? 256 : 64;
     if (dtype == NIB_F32)
-        embed_kernel<float><<<m, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, nib_trace_buffer(), nib_trace_capacity());
+        embed_kernel<float><<<m, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, scale, nib_trace_buffer(), nib_trace_capacity());
     else if (dtype == NIB_BF16)
-        embed_kernel<__nv_bfloat16><<<m, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, nib_trace_buffer(), nib_trace_capacity());
+        embed_kernel<__nv_bfloat16><<<m, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, scale, nib_trace_buffer(), nib_trace_capacity());
     else
         NIB_REQUIRE(false, "embed: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();
     return 0;
+}
+
+NIB_API int nib_embed(const int* ids, const void* table, float* out, int m, int hidden, int vocab,
+                      int dtype, cudaStream_t stream) {
+    return nib_embed_scaled(ids, table, out, m, hidden, vocab, dtype, 1.0f, stream);
 }
 
 // ---------------------------------------------------------------------------------- RMSNorm

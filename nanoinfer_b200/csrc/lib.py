@@ -84,7 +84,9 @@ class Kernels:
                      "nib_delta_rule_scan", "nib_causal_conv", "nib_rglru_scan", "nib_latent_store", "nib_latent_query",
                      "nib_latent_attention", "nib_latent_value", "nib_latent_attention_mma", "nib_latent_attention_mma_supported",
                      "nib_latent_attention_mma_qwidth", "nib_block_diag_smallm", "nib_rmsnorm_pair", "nib_rmsnorm_pair_supported", "nib_head_product_supported",
-                     "nib_head_product_nk", "nib_head_product_kn", "nib_depth_mix_norm_pair"):
+                     "nib_head_product_nk", "nib_head_product_kn", "nib_depth_mix_norm_pair", "nib_embed_scaled", "nib_gated_norm",
+                     "nib_linear_state_scan", "nib_conv_tokens", "nib_conv_tail", "nib_token_shift", "nib_decay_map", "nib_step_sizes",
+                     "nib_attention_prepare", "nib_attention_flex"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -164,11 +166,12 @@ class Kernels:
         return self._lib.nib_device_arch()
 
     # ---- kernels ----------------------------------------------------------------------------
-    def embed(self, ids, table, out32):
+    def embed(self, ids, table, out32, scale=1.0):
+        """out32[t] = table[ids[t]] * scale."""
         _need(ids, torch.int32, "embed ids"); _need(table, None, "embed table"); _need(out32, torch.float32, "embed out")
         m, hidden = out32.shape
-        self._check(self._lib.nib_embed(_ptr(ids), _ptr(table), _ptr(out32), c_int(m), c_int(hidden),
-                                        c_int(table.shape[0]), c_int(_DT[table.dtype]), self._stream()), "embed")
+        self._check(self._lib.nib_embed_scaled(_ptr(ids), _ptr(table), _ptr(out32), c_int(m), c_int(hidden),
+                                               c_int(table.shape[0]), c_int(_DT[table.dtype]), c_float(scale), self._stream()), "embed")
 
     def rmsnorm(self, x32, gain32, eps, out, rows=None):
         _need(x32, torch.float32, "rmsnorm x"); _need(gain32, torch.float32, "rmsnorm gain"); _need(out, None, "rmsnorm out")
@@ -661,6 +664,191 @@ class Kernels:
             return
         for b in range(nb):
             self.linear(a_blocks[b], w_blocks[b], None if bias32 is None else bias32[b], out32[b], "f32")
+
+    # ---- gate, norm in groups, skip (pointwise.cu) ---------------------------------------------------------
+    def gated_norm(self, o32, out, groups=0, eps=0.0, gain32=None, gate32=None, gate_kind="none", gate_first=False,
+                   skip32=None, skip_coef32=None, out_scale=1.0):
+        """Row by row: y = o32 (+ skip_coef32[head of c] * skip32); times act(gate32) if ``gate_first``; with ``groups`` > 0
+        divided by the root mean square of each of ``groups`` equal parts (``eps`` inside the root); times ``gain32`` (a gain
+        per channel, or one of a part's size shared by the parts); times act(gate32) if not ``gate_first``; times
+        ``out_scale``. gate_kind: 'none' | 'sigmoid' | 'silu'. ``skip_coef32`` holds one coefficient per head."""
+        self._rows(o32, torch.float32, "gated_norm o"); self._rows(out, None, "gated_norm out")
+        m, n = o32.shape
+        if tuple(out.shape) != (m, n):
+            raise KernelError("gated_norm: shapes do not fit")
+        kind = {"none": 0, "sigmoid": 1, "silu": 2}[gate_kind]
+        if (kind != 0) != (gate32 is not None) or (skip32 is None) != (skip_coef32 is None):
+            raise KernelError("gated_norm: a gate needs its kind, a skip its coefficients")
+        for t, what in ((gate32, "gate"), (skip32, "skip")):
+            if t is not None:
+                self._rows(t, torch.float32, f"gated_norm {what}")
+                if tuple(t.shape) != (m, n):
+                    raise KernelError(f"gated_norm: {what} does not fit")
+        for t, what in ((gain32, "gain"), (skip_coef32, "skip coefficients")):
+            if t is not None:
+                _need(t, torch.float32, f"gated_norm {what}")
+        norm = 1 if groups else 0
+        if not groups:      # no norm: any split of the row will do; parts of up to 256 channels keep the warps short
+            groups = next(g for g in range(max(1, n // 256), 0, -1) if n % g == 0)
+        if gain32 is not None and gain32.numel() not in (n, n // groups):
+            raise KernelError("gated_norm: the gain has neither a row's size nor a part's")
+        self._check(self._lib.nib_gated_norm(
+            _ptr(o32), c_int(o32.stride(0)), _ptr(gate32), c_int(0 if gate32 is None else gate32.stride(0)), c_int(kind),
+            c_int(1 if gate_first else 0), _ptr(gain32), c_int(0 if gain32 is None else gain32.numel()), _ptr(skip32),
+            c_int(0 if skip32 is None else skip32.stride(0)), _ptr(skip_coef32), c_int(0 if skip_coef32 is None else skip_coef32.numel()),
+            c_int(groups), c_int(norm), c_float(eps), c_float(out_scale), _ptr(out), c_int(out.stride(0)), c_int(m), c_int(n),
+            c_int(_DT[out.dtype]), self._stream()), "gated_norm")
+
+    # ---- matrix states that decay (linear_state.cu) -------------------------------------------------------
+    @staticmethod
+    def _state_row(state, off, size, what):
+        """A state tensor [slots, n] of floats whose rows are dense (a slice of a wider state's columns will do)."""
+        _need(state, torch.float32, what, contiguous=False)
+        if state.dim() != 2 or state.stride(1) != 1 or off < 0 or off + size > state.shape[1]:
+            raise KernelError(f"{what}: the state does not hold {size} floats from column {off}")
+
+    def linear_state_scan(self, q32, k32, v32, w32, state, state_off, ctx, o32, heads, kq_heads, dk, dv, q_scale=1.0,
+                          bonus32=None, v_scale32=None):
+        """Per request and head, over the step's tokens in order, from and into ``state[slot, state_off:]`` (laid out
+        [head, value channel, key channel]): S <- diag(w) S + k (v_scale v)^T, o = S^T (q_scale q); with ``bonus32``
+        [heads, dk] instead o = (S_old + diag(bonus) k v^T)^T q before the update. q32, k32: [tokens, kq_heads * dk]
+        (head h reads key head h // (heads / kq_heads)); v32, o32: [tokens, heads * dv]; w32: [tokens, heads * dk] (a
+        decay per key channel) or [tokens, heads] (one per head); v_scale32: [tokens, heads]."""
+        for t, what, width in ((q32, "q", kq_heads * dk), (k32, "k", kq_heads * dk), (v32, "v", heads * dv), (o32, "o", heads * dv)):
+            self._rows(t, torch.float32, f"linear_state_scan {what}")
+            if tuple(t.shape) != (q32.shape[0], width):
+                raise KernelError(f"linear_state_scan: {what} does not fit")
+        self._rows(w32, torch.float32, "linear_state_scan w")
+        if w32.shape[0] != q32.shape[0] or w32.shape[1] not in (heads * dk, heads):
+            raise KernelError("linear_state_scan: the decay is neither per key channel nor per head")
+        per_channel = w32.shape[1] == heads * dk and not (dk == 1 and w32.shape[1] == heads)
+        if bonus32 is not None:
+            _need(bonus32, torch.float32, "linear_state_scan bonus")
+            if bonus32.numel() != heads * dk:
+                raise KernelError("linear_state_scan: the bonus does not fit")
+        if v_scale32 is not None:
+            _need(v_scale32, torch.float32, "linear_state_scan v_scale")
+            if tuple(v_scale32.shape) != (q32.shape[0], heads):
+                raise KernelError("linear_state_scan: v_scale does not fit")
+        self._state_row(state, state_off, heads * dv * dk, "linear_state_scan state")
+        self._check(self._lib.nib_linear_state_scan(
+            _ptr(q32), c_int(q32.stride(0)), _ptr(k32), c_int(k32.stride(0)), _ptr(v32), c_int(v32.stride(0)), _ptr(w32),
+            c_int(w32.stride(0)), c_int(1 if per_channel else 0), _ptr(bonus32), _ptr(v_scale32), _ptr(state), c_longlong(state.stride(0)),
+            c_int(state_off), _ptr(ctx.q_start), _ptr(ctx.state_slots), _ptr(o32), c_int(o32.stride(0)), c_int(ctx.host.num_requests),
+            c_int(heads), c_int(kq_heads), c_int(dk), c_int(dv), c_float(q_scale), self._stream()), "linear_state_scan")
+
+    def conv_tokens(self, x32, w32, bias32, act, state, state_off, ctx, out32, taps):
+        """out32[t, c] = act(bias32[c] + sum_j w32[c, j] * x32[t - (taps-1-j), c]) within each request; inputs before the
+        step's first token come from ``state[slot, state_off + i * width + c]`` (i = 0 oldest). act: 'none' | 'silu'."""
+        self._rows(x32, torch.float32, "conv_tokens x"); self._rows(out32, torch.float32, "conv_tokens out"); _need(w32, torch.float32, "conv_tokens w")
+        m, width = x32.shape
+        if tuple(w32.shape) != (width, taps) or tuple(out32.shape) != (m, width) or (bias32 is not None and bias32.numel() != width):
+            raise KernelError("conv_tokens: shapes do not fit")
+        if bias32 is not None:
+            _need(bias32, torch.float32, "conv_tokens bias")
+        if taps > 1:
+            self._state_row(state, state_off, (taps - 1) * width, "conv_tokens state")
+        self._check(self._lib.nib_conv_tokens(
+            _ptr(x32), c_int(x32.stride(0)), _ptr(w32), _ptr(bias32), c_int({"none": 0, "silu": 1}[act]), _ptr(state if taps > 1 else None),
+            c_longlong(state.stride(0) if taps > 1 else 0), c_int(state_off), _ptr(ctx.q_start), _ptr(ctx.req_index), _ptr(ctx.state_slots),
+            _ptr(out32), c_int(out32.stride(0)), c_int(m), c_int(width), c_int(taps), self._stream()), "conv_tokens")
+
+    def conv_tail(self, x32, state, state_off, ctx, taps):
+        """The state's history rows become each request's last taps-1 rows of x32 (older rows move up when the step brought
+        fewer). Runs after ``conv_tokens`` of the same step has read them."""
+        self._rows(x32, torch.float32, "conv_tail x")
+        self._state_row(state, state_off, (taps - 1) * x32.shape[1], "conv_tail state")
+        self._check(self._lib.nib_conv_tail(_ptr(x32), c_int(x32.stride(0)), _ptr(state), c_longlong(state.stride(0)), c_int(state_off),
+                                            _ptr(ctx.q_start), _ptr(ctx.state_slots), c_int(ctx.host.num_requests), c_int(x32.shape[1]),
+                                            c_int(taps), self._stream()), "conv_tail")
+
+    def token_shift(self, h, mu32, state, state_off, ctx, mixes):
+        """mixes[s, t] = h[t] + (h[t-1] - h[t]) * mu32[s]; the token before a request's first one in the step is
+        ``state[slot, state_off:]``, which then becomes the request's last h."""
+        _need(h, None, "token_shift h"); _need(mu32, torch.float32, "token_shift mu"); _need(mixes, h.dtype, "token_shift out")
+        m, width = h.shape
+        if mu32.dim() != 2 or mu32.shape[1] != width or tuple(mixes.shape) != (mu32.shape[0], m, width):
+            raise KernelError("token_shift: shapes do not fit")
+        self._state_row(state, state_off, width, "token_shift state")
+        self._check(self._lib.nib_token_shift(_ptr(h), _ptr(mu32), c_int(mu32.shape[0]), _ptr(state), c_longlong(state.stride(0)), c_int(state_off),
+                                              _ptr(ctx.q_start), _ptr(ctx.req_index), _ptr(ctx.state_slots), _ptr(mixes), c_int(m), c_int(width),
+                                              c_int(_DT[h.dtype]), self._stream()), "token_shift")
+
+    def decay_map(self, z32, out32, kind, param):
+        """kind 'sigmoid_root': sigmoid(z)^(1/param); 'exp_neg_exp': exp(-exp(z)). Rounded to 32 bits once."""
+        self._rows(z32, torch.float32, "decay_map z"); self._rows(out32, torch.float32, "decay_map out")
+        if z32.shape != out32.shape:
+            raise KernelError("decay_map: shapes differ")
+        self._check(self._lib.nib_decay_map(_ptr(z32), c_int(z32.stride(0)), _ptr(out32), c_int(out32.stride(0)), c_int(z32.shape[0]),
+                                            c_int(z32.shape[1]), c_int({"sigmoid_root": 0, "exp_neg_exp": 1}[kind]), c_float(param),
+                                            self._stream()), "decay_map")
+
+    def step_sizes(self, dt_raw32, dt_bias32, a_log32, dt_out, decay_out):
+        """dt_out = softplus(dt_raw32 + dt_bias32), decay_out = exp(-exp(a_log32) * dt_out), per (token, head)."""
+        self._rows(dt_raw32, torch.float32, "step_sizes dt"); _need(dt_bias32, torch.float32, "step_sizes bias"); _need(a_log32, torch.float32, "step_sizes A")
+        _need(dt_out, torch.float32, "step_sizes out"); _need(decay_out, torch.float32, "step_sizes out")
+        m, heads = dt_raw32.shape
+        if dt_bias32.numel() != heads or a_log32.numel() != heads or tuple(dt_out.shape) != (m, heads) or tuple(decay_out.shape) != (m, heads):
+            raise KernelError("step_sizes: shapes do not fit")
+        self._check(self._lib.nib_step_sizes(_ptr(dt_raw32), c_int(dt_raw32.stride(0)), _ptr(dt_bias32), _ptr(a_log32), _ptr(dt_out), _ptr(decay_out),
+                                             c_int(m), c_int(heads), self._stream()), "step_sizes")
+
+    # ---- attention with options (attention_flex.cu) --------------------------------------------------------
+    def attention_prepare(self, qkv32, q_out, heads, kv_heads, dim, vdim, q_gain32, k_gain32, eps, freq32, rot_dims, ctx,
+                          block_table, page_size, k_pages, v_pages, writes):
+        """From the 32-bit rows [q | k | v]: optional per-head RMS norm of q and k (gains of ``dim``), rotation of the first
+        ``rot_dims`` elements of every q and k head by position * freq32, queries into ``q_out`` in the storage type, and
+        with ``writes`` keys and values into their pages."""
+        self._rows(qkv32, torch.float32, "attention_prepare qkv"); _need(q_out, None, "attention_prepare q")
+        m = qkv32.shape[0]
+        if qkv32.shape[1] != (heads + kv_heads) * dim + kv_heads * vdim or tuple(q_out.shape) != (m, heads * dim):
+            raise KernelError("attention_prepare: widths do not fit the head counts")
+        for t in (q_gain32, k_gain32):
+            if t is not None:
+                _need(t, torch.float32, "attention_prepare gain")
+                if t.numel() != dim:
+                    raise KernelError("attention_prepare: a gain has the size of a head")
+        if rot_dims:
+            _need(freq32, torch.float32, "attention_prepare freq")
+            if freq32.numel() != rot_dims // 2:
+                raise KernelError("attention_prepare: one frequency per rotated pair")
+        num_pages = bt_stride = 0
+        if writes:
+            _need(block_table, torch.int32, "block_table", contiguous=False)
+            _need(k_pages, q_out.dtype, "k_pages"); _need(v_pages, q_out.dtype, "v_pages")
+            if tuple(k_pages.shape[1:]) != (kv_heads, page_size, dim) or tuple(v_pages.shape[1:]) != (kv_heads, page_size, vdim) \
+                    or block_table.stride(1) != 1 or v_pages.shape[0] != k_pages.shape[0]:
+                raise KernelError("attention_prepare: pages or block table do not fit")
+            num_pages, bt_stride = k_pages.shape[0], block_table.stride(0)
+        self._check(self._lib.nib_attention_prepare(
+            _ptr(qkv32), c_int(qkv32.stride(0)), _ptr(q_out), _ptr(q_gain32), _ptr(k_gain32), c_float(eps), _ptr(freq32 if rot_dims else None),
+            c_int(rot_dims), _ptr(ctx.positions), _ptr(ctx.req_index), _ptr(block_table if writes else None), c_int(bt_stride), c_int(page_size),
+            _ptr(k_pages if writes else None), _ptr(v_pages if writes else None), c_int(num_pages), c_int(m), c_int(heads), c_int(kv_heads),
+            c_int(dim), c_int(vdim), c_int(1 if writes else 0), c_int(_DT[q_out.dtype]), self._stream()), "attention_prepare")
+
+    def attention_flex(self, q, out, heads, kv_heads, dim, vdim, scale, softcap, slopes32, window, chunk, out_scale, ctx,
+                       block_table, page_size, k_pages, v_pages):
+        """Softmax attention of every token of the step over its request's cached keys: j <= own position, within
+        ``window`` (0 = none) and within the own block of ``chunk`` positions (0 = none); score = (q . k) * scale, capped
+        by ``softcap`` * tanh(. / softcap) (0 = none), minus slopes32[head] * distance (None = none). ``out``
+        [tokens, heads * vdim] in float or the storage type, times ``out_scale``."""
+        _need(q, None, "attention q"); _need(out, None, "attention out")
+        _need(k_pages, q.dtype, "k_pages"); _need(v_pages, q.dtype, "v_pages"); _need(block_table, torch.int32, "block_table", contiguous=False)
+        m = q.shape[0]
+        if tuple(k_pages.shape[1:]) != (kv_heads, page_size, dim) or tuple(v_pages.shape[1:]) != (kv_heads, page_size, vdim) \
+                or q.shape[1] != heads * dim or tuple(out.shape) != (m, heads * vdim) or block_table.stride(1) != 1:
+            raise KernelError("attention_flex: shapes do not fit")
+        if out.dtype not in (torch.float32, q.dtype):
+            raise KernelError("attention_flex: out is float or of the storage type")
+        if slopes32 is not None:
+            _need(slopes32, torch.float32, "attention slopes")
+            if slopes32.numel() != heads:
+                raise KernelError("attention_flex: one slope per head")
+        self._check(self._lib.nib_attention_flex(
+            _ptr(q), c_int(q.stride(0)), _ptr(out), c_int(1 if out.dtype == torch.float32 else 0), _ptr(ctx.positions), _ptr(ctx.req_index),
+            _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(k_pages.shape[0]), c_int(m),
+            c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_float(scale), c_float(softcap), _ptr(slopes32), c_int(window), c_int(chunk),
+            c_float(out_scale), c_int(_DT[q.dtype]), self._stream()), "attention (options)")
 
     # ---- recurrent mixers (recurrent.cu) -------------------------------------------------------------
     def delta_rule_scan(self, r32, k32, v32, a_logit32, w_logit32, state, ctx, o32, heads, d):

@@ -394,3 +394,76 @@ NIB_API int nib_depth_mix_norm_pair(float* hist, float* x, const float* coef, in
 #undef NIB_DP
     return 0;
 }
+
+// ---------------------------------------------------------------------------------- gate, norm in groups, skip
+// For a row o of n floats cut into `groups` equal parts (a warp per (token, part)):
+//     y = o (+ coef[c / (n / n_coef)] * skip)          a skip connection with one coefficient per head
+//     y = y * act(gate)                                 if gate_first
+//     y = y / sqrt(mean_part(y^2) + eps)                if norm
+//     y = y * gain[c % gain_len]                        gain_len = n (a gain per channel) or a part's size (shared)
+//     y = y * act(gate)                                 if not gate_first
+//     out = y * out_scale
+// act: 1 sigmoid, 2 silu, 0 none. With norm the part is read twice (sum of squares, then the result).
+__device__ __forceinline__ float gate_act(float g, int kind) {
+    const float s = 1.0f / (1.0f + expf(-g));
+    return kind == 1 ? s : g * s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+gated_norm_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ gate, int ldg, int gate_kind, int gate_first,
+                  const float* __restrict__ gain, int gain_len, const float* __restrict__ skip, int lds,
+                  const float* __restrict__ coef, int coef_span, int norm, float eps, float out_scale,
+                  T* __restrict__ out, int ld_out, int tokens, int groups, int width) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (w >= (long long)tokens * groups) return;
+    const int t = (int)(w / groups), c0 = (int)(w % groups) * width;
+    const float* orow = o + (size_t)t * ldo;
+    const float* grow = gate != nullptr ? gate + (size_t)t * ldg : nullptr;
+    const float* srow = skip != nullptr ? skip + (size_t)t * lds : nullptr;
+    const bool early = grow != nullptr && gate_kind != 0 && gate_first != 0;
+    const bool late = grow != nullptr && gate_kind != 0 && gate_first == 0;
+    float scale = 1.0f;
+    if (norm) {
+        float ss = 0.f;
+        for (int j = lane; j < width; j += 32) {
+            const int c = c0 + j;
+            float y = orow[c];
+            if (srow != nullptr) y = fmaf(coef[c / coef_span], srow[c], y);
+            if (early) y *= gate_act(grow[c], gate_kind);
+            ss = fmaf(y, y, ss);
+        }
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)width + eps);
+    }
+    for (int j = lane; j < width; j += 32) {
+        const int c = c0 + j;
+        float y = orow[c];
+        if (srow != nullptr) y = fmaf(coef[c / coef_span], srow[c], y);
+        if (early) y *= gate_act(grow[c], gate_kind);
+        y *= scale;
+        if (gain != nullptr) y *= gain[c % gain_len];
+        if (late) y *= gate_act(grow[c], gate_kind);
+        Elem<T>::store(out + (size_t)t * ld_out + c, y * out_scale);
+    }
+}
+
+NIB_API int nib_gated_norm(const float* o, int ldo, const float* gate, int ldg, int gate_kind, int gate_first, const float* gain,
+                           int gain_len, const float* skip, int lds, const float* coef, int n_coef, int groups, int norm, float eps,
+                           float out_scale, void* out, int ld_out, int tokens, int n, int dtype, cudaStream_t stream) {
+    NIB_REQUIRE(tokens >= 0 && n > 0 && groups > 0 && n % groups == 0, "gated_norm: %d channels do not split into %d parts", n, groups);
+    NIB_REQUIRE(gain == nullptr || (gain_len > 0 && n % gain_len == 0), "gated_norm: a gain of %d does not tile %d channels", gain_len, n);
+    NIB_REQUIRE(skip == nullptr || (coef != nullptr && n_coef > 0 && n % n_coef == 0), "gated_norm: bad skip coefficients");
+    NIB_REQUIRE(gate_kind >= 0 && gate_kind <= 2, "gated_norm: unknown gate kind %d", gate_kind);
+    if (tokens == 0) return 0;
+    const int width = n / groups, span = skip != nullptr ? n / n_coef : 1;
+    const int blocks = ceil_div((long long)tokens * groups, 4);
+    if (dtype == NIB_F32) NIB_CUDA(launch_pdl(gated_norm_kernel<float>, dim3(blocks), dim3(128), (size_t)(0), stream, o, ldo, gate, ldg, gate_kind, gate_first, gain, gain_len, skip, lds, coef, span, norm, eps, out_scale, (float*)out, ld_out, tokens, groups, width));
+    else if (dtype == NIB_BF16) NIB_CUDA(launch_pdl(gated_norm_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), (size_t)(0), stream, o, ldo, gate, ldg, gate_kind, gate_first, gain, gain_len, skip, lds, coef, span, norm, eps, out_scale, (__nv_bfloat16*)out, ld_out, tokens, groups, width));
+    else NIB_REQUIRE(false, "gated_norm: unknown dtype %d", dtype);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
