@@ -86,7 +86,7 @@ class Kernels:
                      "nib_latent_attention_mma_qwidth", "nib_block_diag_smallm", "nib_rmsnorm_pair", "nib_rmsnorm_pair_supported", "nib_head_product_supported",
                      "nib_head_product_nk", "nib_head_product_kn", "nib_depth_mix_norm_pair", "nib_embed_scaled", "nib_gated_norm",
                      "nib_linear_state_scan", "nib_conv_tokens", "nib_conv_tail", "nib_token_shift", "nib_decay_map", "nib_step_sizes",
-                     "nib_attention_prepare", "nib_attention_flex"):
+                     "nib_attention_prepare", "nib_attention_flex", "nib_attention_flex_mma", "nib_attention_flex_mma_supported"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -844,6 +844,15 @@ class Kernels:
             _need(slopes32, torch.float32, "attention slopes")
             if slopes32.numel() != heads:
                 raise KernelError("attention_flex: one slope per head")
+        if q.dtype == torch.bfloat16 and not self.options.force_general_attention and page_size > 0 \
+                and self._lib.nib_attention_flex_mma_supported(c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(q.stride(0))) == 1:
+            # bfloat16 heads of up to 128 (multiples of 8): tensor cores, prompt portions and decoded tokens alike
+            self._check(self._lib.nib_attention_flex_mma(
+                _ptr(q), c_int(q.stride(0)), _ptr(out), c_int(1 if out.dtype == torch.float32 else 0), _ptr(ctx.q_start), _ptr(ctx.ctx_lens),
+                _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(k_pages.shape[0]),
+                c_int(ctx.host.num_requests), c_int(max(ctx.host.q_lens)), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_float(scale),
+                c_float(softcap), _ptr(slopes32), c_int(window), c_int(chunk), c_float(out_scale), self._stream()), "attention (options, tensor cores)")
+            return
         self._check(self._lib.nib_attention_flex(
             _ptr(q), c_int(q.stride(0)), _ptr(out), c_int(1 if out.dtype == torch.float32 else 0), _ptr(ctx.positions), _ptr(ctx.req_index),
             _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(k_pages.shape[0]), c_int(m),

@@ -250,7 +250,7 @@ def test_prepare_norms_rotates_and_writes_pages(ops, dtype, heads, kv, dk, dv, r
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("opts", [dict(), dict(chunk=7), dict(chunk=32), dict(chunk=33, slopes=True), dict(window=9), dict(softcap=2.0),
                                   dict(softcap=20.0, slopes=True, chunk=120), dict(window=40, chunk=64)])
-@pytest.mark.parametrize("heads,kv,dk,dv,page", [(3, 1, 12, 8, 4), (4, 2, 96, 64, 16), (2, 2, 40, 100, 8)])
+@pytest.mark.parametrize("heads,kv,dk,dv,page", [(3, 1, 12, 8, 4), (4, 2, 96, 64, 16), (2, 2, 40, 104, 8), (8, 1, 128, 128, 16), (2, 2, 36, 100, 8)])
 def test_attention_over_pages_with_options(ops, dtype, opts, heads, kv, dk, dv, page):
     """Prompt portions beside decoded tokens over contexts that span pages, chunks and windows; float and storage-type
     outputs; an output factor."""
@@ -268,10 +268,12 @@ def test_attention_over_pages_with_options(ops, dtype, opts, heads, kv, dk, dv, 
     ref = torch.empty(sum(q_lens), heads * dv, dtype=torch.float64)
     TorchOps().attention_flex(q.cpu(), ref, *args[:6], None if slopes is None else slopes.cpu(), *args[7:], 0.8, to_cpu(ctx), full_bt.cpu(),
                               page, kp.cpu(), vp.cpu())
-    for out_dtype in {torch.float32, dtype}:
-        out = torch.empty(sum(q_lens), heads * dv, dtype=out_dtype, device=DEV)
-        ops.attention_flex(q, out, *args, 0.8, ctx, full_bt, page, kp, vp)
-        assert_close(out, ref, dtype, f"{opts} out {out_dtype}")
+    paths = [ops] if dtype == torch.float32 else [ops, ops.with_options(force_general_attention=True)]      # tensor cores; the general kernel
+    for k in paths:
+        for out_dtype in {torch.float32, dtype}:
+            out = torch.empty(sum(q_lens), heads * dv, dtype=out_dtype, device=DEV)
+            k.attention_flex(q, out, *args, 0.8, ctx, full_bt, page, kp, vp)
+            assert_close(out, ref, dtype, f"{opts} out {out_dtype} general {k is not ops}")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
