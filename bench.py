@@ -500,9 +500,38 @@ def design_configs(size: dict):
     return nez, qwen
 
 
+# A Vafozen stack at the same widths: chunked softmax attention beside gated linear attention, a state-space mixer,
+# rotated and capped softmax attention beside a time mix, a state-space mixer, twice; SwiGLU feed-forwards of the Qwen2
+# decoder's size; the softmax halves have the Qwen2 decoder's head counts and head size.
+VAFOZEN_SIZES = {
+    "1k": {"width": 1024, "heads": 16, "head_dim": 64, "ff_swiglu": 2816, "rot": 32, "side_heads": 4, "decay_rank": 64,
+           "ssm_heads": 32, "ssm_state": 128, "chunk": 1024, "vocab": 32000, "layers": 8},
+    "2k": {"width": 2048, "heads": 16, "head_dim": 128, "ff_swiglu": 5632, "rot": 64, "side_heads": 4, "decay_rank": 64,
+           "ssm_heads": 32, "ssm_state": 128, "chunk": 1024, "vocab": 32000, "layers": 8},
+}
+
+
+def vafozen_configs(size: dict):
+    w, h, d = size["width"], size["heads"], size["head_dim"]
+    ff = {"kind": "dense", "ff": size["ff_swiglu"]}
+    side = {"heads": size["side_heads"], "dim": d, "decay_rank": size["decay_rank"]}
+    chunked = {"heads": h, "kv_heads": 2, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": size["chunk"]}}
+    rotated = {"heads": h, "kv_heads": 2, "dim": d, "vdim": d, "scale": d ** -0.5, "conv": 4, "softcap": 30.0,
+               "rot": {"dims": size["rot"], "base": 10000.0}}
+    kinds = [
+        {"type": "parallel", "mixer": {"left": chunked, "right": dict(side, tau=16.0), "left_scale": 1.0, "right_scale": 1.0}, "mlp": ff},
+        {"type": "mamba2", "mixer": {"heads": size["ssm_heads"], "vdim": 2 * w // size["ssm_heads"], "state": size["ssm_state"], "groups": 2,
+                                     "norm_groups": 2, "conv": 4}, "mlp": ff},
+        {"type": "parallel_2", "mixer": {"left": rotated, "right": dict(side), "left_scale": 1.0, "right_scale": 1.0}, "mlp": ff},
+    ]
+    layers = [kinds[(0, 1, 2, 1)[i % 4]] for i in range(size["layers"])]
+    vaf = {"architecture": "Vafozen", "vocab": size["vocab"], "width": w, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "layers": layers}
+    return vaf, design_configs(dict(DESIGN_SIZES["1k"], **{k: size[k] for k in ("width", "heads", "head_dim", "ff_swiglu", "vocab", "layers")}))[1]
+
+
 def run_design(args) -> dict:
-    """Prefill and decode throughput of the Nezalorn design beside the Qwen2 decoder at equal size (random weights,
-    bfloat16, device-timed with CUDA events), and where one eager step's time goes, launch kind by launch kind."""
+    """Prefill and decode throughput of a design (Nezalorn, Vafozen) beside the Qwen2 decoder at equal size (random
+    weights, bfloat16, device-timed with CUDA events), and where one eager step's time goes, launch kind by launch kind."""
     import numpy as np
     import torch
     from nanoinfer_b200 import load_model
@@ -512,13 +541,15 @@ def run_design(args) -> dict:
     pk = peaks()
     t_pre, batch, ctx = args.prefill_tokens, args.batch, min(args.context, 2048)
     steps, warmup = min(args.steps, 64), max(3, args.warmup)
-    out = {"impl": "ours", "design": "nezalorn", "dtype": "bf16", "data": "synthetic: seeded random weights and random token ids",
+    design = args.design
+    sizes, configs = {"nezalorn": (DESIGN_SIZES, design_configs), "vafozen": (VAFOZEN_SIZES, vafozen_configs)}[design]
+    out = {"impl": "ours", "design": design, "dtype": "bf16", "data": "synthetic: seeded random weights and random token ids",
            "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]},
            "config": {"prefill_tokens": t_pre, "decode_batch": batch, "decode_context": ctx, "page_size": 16}, "sizes": {}}
-    for name in (args.design_sizes.split(",") if args.design_sizes else sorted(DESIGN_SIZES)):
-        size = DESIGN_SIZES[name]
+    for name in (args.design_sizes.split(",") if args.design_sizes else sorted(sizes)):
+        size = sizes[name]
         row = {}
-        for label, cfg_json in zip(("nezalorn", "qwen2"), design_configs(size)):
+        for label, cfg_json in zip((design, "qwen2"), configs(size)):
             rng = np.random.default_rng(0)
             tmp = tempfile.mkdtemp(prefix="nanoinfer_b200_design_")
             try:
@@ -603,8 +634,8 @@ def run_design(args) -> dict:
                 row[label]["launch_kinds_us"] = kinds
             del model, engine, ops
             torch.cuda.empty_cache()
-        row["ratio_prefill"] = round(row["nezalorn"]["prefill_tok_s"] / row["qwen2"]["prefill_tok_s"], 3)
-        row["ratio_decode"] = round(row["nezalorn"]["decode_tok_s"] / row["qwen2"]["decode_tok_s"], 3)
+        row["ratio_prefill"] = round(row[design]["prefill_tok_s"] / row["qwen2"]["prefill_tok_s"], 3)
+        row["ratio_decode"] = round(row[design]["decode_tok_s"] / row["qwen2"]["decode_tok_s"], 3)
         out["sizes"][name] = dict(row, size=size)
     return out
 
@@ -743,7 +774,7 @@ def main() -> int:
                     help="add a 'kernels' block: where the time of a decode step and of a prompt portion goes, kernel kind by "
                          "kind, with bytes or FLOPs and the fraction of the measured peak")
     ap.add_argument("--shape", default="0.5b", choices=sorted(SHAPES), help="layer sizes: the family's 0.5B (default), 1.5B or 7B")
-    ap.add_argument("--design", default=None, choices=["nezalorn"],
+    ap.add_argument("--design", default=None, choices=["nezalorn", "vafozen"],
                     help="instead of the headline workload: prefill and decode throughput of this design beside the Qwen2 "
                          "decoder at equal size (--design-sizes, --prefill-tokens, --batch, --context up to 2048, --breakdown)")
     ap.add_argument("--design-sizes", default="", help="comma-separated names of DESIGN_SIZES (default: all)")

@@ -85,7 +85,7 @@ class Kernels:
                      "nib_latent_attention", "nib_latent_value", "nib_latent_attention_mma", "nib_latent_attention_mma_supported",
                      "nib_latent_attention_mma_qwidth", "nib_block_diag_smallm", "nib_rmsnorm_pair", "nib_rmsnorm_pair_supported", "nib_head_product_supported",
                      "nib_head_product_nk", "nib_head_product_kn", "nib_depth_mix_norm_pair", "nib_embed_scaled", "nib_gated_norm",
-                     "nib_linear_state_scan", "nib_conv_tokens", "nib_conv_tail", "nib_token_shift", "nib_decay_map", "nib_step_sizes",
+                     "nib_linear_state_scan", "nib_conv_tokens", "nib_conv_tail", "nib_conv_step", "nib_token_shift", "nib_decay_map", "nib_step_sizes",
                      "nib_attention_prepare", "nib_attention_flex", "nib_attention_flex_mma", "nib_attention_flex_mma_supported"):
             getattr(self._lib, name).restype = c_int
 
@@ -761,6 +761,27 @@ class Kernels:
         self._check(self._lib.nib_conv_tail(_ptr(x32), c_int(x32.stride(0)), _ptr(state), c_longlong(state.stride(0)), c_int(state_off),
                                             _ptr(ctx.q_start), _ptr(ctx.state_slots), c_int(ctx.host.num_requests), c_int(x32.shape[1]),
                                             c_int(taps), self._stream()), "conv_tail")
+
+    def conv_step(self, x32, w32, bias32, act, state, state_off, ctx, out32, taps):
+        """``conv_tokens`` followed by ``conv_tail``: the convolution of the step's tokens, then the history moves on. Steps
+        in which no request brings more than 16 tokens (a decode step) take one launch for both."""
+        if max(ctx.host.q_lens) > 16 or taps > 16:
+            self.conv_tokens(x32, w32, bias32, act, state, state_off, ctx, out32, taps)
+            if taps > 1:
+                self.conv_tail(x32, state, state_off, ctx, taps)
+            return
+        self._rows(x32, torch.float32, "conv_step x"); self._rows(out32, torch.float32, "conv_step out"); _need(w32, torch.float32, "conv_step w")
+        m, width = x32.shape
+        if tuple(w32.shape) != (width, taps) or tuple(out32.shape) != (m, width) or (bias32 is not None and bias32.numel() != width):
+            raise KernelError("conv_step: shapes do not fit")
+        if bias32 is not None:
+            _need(bias32, torch.float32, "conv_step bias")
+        if taps > 1:
+            self._state_row(state, state_off, (taps - 1) * width, "conv_step state")
+        self._check(self._lib.nib_conv_step(
+            _ptr(x32), c_int(x32.stride(0)), _ptr(w32), _ptr(bias32), c_int({"none": 0, "silu": 1}[act]), _ptr(state if taps > 1 else None),
+            c_longlong(state.stride(0) if taps > 1 else 0), c_int(state_off), _ptr(ctx.q_start), _ptr(ctx.state_slots), _ptr(out32),
+            c_int(out32.stride(0)), c_int(ctx.host.num_requests), c_int(width), c_int(taps), self._stream()), "conv_step")
 
     def token_shift(self, h, mu32, state, state_off, ctx, mixes):
         """mixes[s, t] = h[t] + (h[t-1] - h[t]) * mu32[s]; the token before a request's first one in the step is

@@ -17,89 +17,166 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------- the walk
-// A block owns 32 value columns of one head of one request; eight lanes share a column, each with C consecutive key
-// channels of the state in registers (8 C >= dk; channels beyond dk hold zeros). The tokens' vectors are staged in
-// shared memory LS_TB at a time. State layout per slot: [head, value channel, key channel].
-constexpr int LS_COLS = 32;
+// A block owns 16 value columns of one head of one request; eight lanes share a column, each with C key channels of the
+// state in registers (8 C >= dk; channels beyond dk hold zeros): lane l owns the channels (8 i + l) * 4 .. + 3, so the
+// eight lanes read 128 consecutive bytes of a token's vector with one 16-byte load each. The tokens' vectors are staged
+// in shared memory TB at a time by cp.async, three chunks ahead of the one that is walked (rows and columns that do not
+// exist arrive as zeros, under which a state element stays zero). What a token costs is 3 C multiply-adds per thread
+// and a share of a butterfly over the eight lanes. State layout per slot: [head, value channel, key channel].
+constexpr int LS_COLS = 16;
 constexpr int LS_LANES = 8;
-constexpr int LS_TB = 8;
 constexpr int LS_THREADS = LS_COLS * LS_LANES;
 
-template <int C>
+__device__ __forceinline__ void ls_cp_async_4(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int n = valid ? 4 : 0;    // 0 source bytes: the destination is zero-filled
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+
+// One staged chunk in shared memory: TB tokens' q and k (DKP floats each), decays (DKP, or one per token), the block's
+// value columns and the factor on the values. STAGES chunks are in flight: a chunk's loads have the walk of the
+// STAGES - 1 chunks before it to arrive.
+template <int C, bool PER_CHANNEL> struct LsLayout {
+    static constexpr int DKP = LS_LANES * C;
+    static constexpr int TB = 8;                        // as many tokens as lanes share a column: see the butterfly below
+    static constexpr int STAGES = C >= 32 ? 2 : 4;
+    static constexpr int WP = PER_CHANNEL ? DKP : 4;
+    static constexpr int K0 = TB * DKP, W0 = 2 * TB * DKP, V0 = W0 + TB * WP, F0 = V0 + TB * LS_COLS;
+    static constexpr int STAGE = F0 + ((TB + 3) / 4) * 4;
+    static constexpr int BYTES = STAGES * STAGE * 4;
+};
+
+template <int C, bool PER_CHANNEL, bool BONUS>
 __global__ void __launch_bounds__(LS_THREADS)
 linear_state_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk, const float* __restrict__ v, int ldv,
-                         const float* __restrict__ w, int ldw, int w_per_channel, const float* __restrict__ bonus,
+                         const float* __restrict__ w, int ldw, const float* __restrict__ bonus,
                          const float* __restrict__ v_scale, float* __restrict__ state, long long state_ld, int state_off,
                          const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ o, int ldo,
                          int heads, int kq_heads, int dk, int dv, float q_scale) {
-    constexpr int DKP = LS_LANES * C;
-    __shared__ __align__(16) float q_s[LS_TB][DKP];
-    __shared__ __align__(16) float k_s[LS_TB][DKP];
-    __shared__ __align__(16) float w_s[LS_TB][DKP];
-    __shared__ float v_s[LS_TB][LS_COLS];
+    using L = LsLayout<C, PER_CHANNEL>;
+    constexpr int DKP = L::DKP, TB = L::TB, STAGES = L::STAGES;
+    extern __shared__ __align__(16) float ls_smem[];
+    auto q_s = [&](int buf, int tt) { return ls_smem + buf * L::STAGE + tt * DKP; };
+    auto k_s = [&](int buf, int tt) { return ls_smem + buf * L::STAGE + L::K0 + tt * DKP; };
+    auto w_s = [&](int buf, int tt) { return ls_smem + buf * L::STAGE + L::W0 + tt * L::WP; };
+    auto v_s = [&](int buf, int tt) { return ls_smem + buf * L::STAGE + L::V0 + tt * LS_COLS; };
+    auto f_s = [&](int buf) { return ls_smem + buf * L::STAGE + L::F0; };
     const int req = blockIdx.z, h = blockIdx.y;
     const int hq = h / (heads / kq_heads);
     const int lane = threadIdx.x & (LS_LANES - 1), col = threadIdx.x / LS_LANES;
     const int j = blockIdx.x * LS_COLS + col;
     const int row0 = q_start[req], row1 = q_start[req + 1];
-    const int c0 = lane * C;
     float* srow = state + (long long)slots[req] * state_ld + state_off + ((long long)h * dv + j) * dk;
     float S[C], U[C];
 #pragma unroll
     for (int i = 0; i < C; ++i) {
-        S[i] = (j < dv && c0 + i < dk) ? srow[c0 + i] : 0.f;
-        U[i] = (bonus != nullptr && c0 + i < dk) ? bonus[(size_t)h * dk + c0 + i] : 0.f;
+        const int c = ((i >> 2) * LS_LANES + lane) * 4 + (i & 3);
+        S[i] = (j < dv && c < dk) ? srow[c] : 0.f;
+        U[i] = (BONUS && c < dk) ? bonus[(size_t)h * dk + c] : 0.f;
     }
-    const bool with_bonus = bonus != nullptr;
-    for (int base = row0; base < row1; base += LS_TB) {
-        const int nt = min(LS_TB, row1 - base);
-        __syncthreads();        // the chunk before has been walked
-        for (int e = threadIdx.x; e < LS_TB * DKP; e += LS_THREADS) {
+    const bool scaled = v_scale != nullptr;
+
+    auto stage = [&](int buf, int base) {
+        const int nt = min(TB, row1 - base);
+        for (int e = threadIdx.x; e < TB * DKP; e += LS_THREADS) {
             const int tt = e / DKP, c = e % DKP;
-            float qv = 0.f, kv = 0.f, wv = 1.f;
-            if (tt < nt && c < dk) {
-                const size_t row = (size_t)(base + tt);
-                qv = q[row * ldq + (size_t)hq * dk + c] * q_scale;
-                kv = k[row * ldk + (size_t)hq * dk + c];
-                wv = w_per_channel ? w[row * ldw + (size_t)h * dk + c] : w[row * ldw + h];
-            }
-            q_s[tt][c] = qv; k_s[tt][c] = kv; w_s[tt][c] = wv;
+            const bool ok = tt < nt && c < dk;
+            const size_t row = (size_t)(base + (ok ? tt : 0));
+            const int cc = ok ? c : 0;
+            ls_cp_async_4(q_s(buf, tt) + c, q + row * ldq + (size_t)hq * dk + cc, ok);
+            ls_cp_async_4(k_s(buf, tt) + c, k + row * ldk + (size_t)hq * dk + cc, ok);
+            if (PER_CHANNEL) ls_cp_async_4(w_s(buf, tt) + c, w + row * ldw + (size_t)h * dk + cc, ok);
         }
-        for (int e = threadIdx.x; e < LS_TB * LS_COLS; e += LS_THREADS) {
+        for (int e = threadIdx.x; e < TB * LS_COLS; e += LS_THREADS) {
             const int tt = e / LS_COLS, cc = e % LS_COLS, jj = blockIdx.x * LS_COLS + cc;
-            float vv = 0.f;
-            if (tt < nt && jj < dv) {
-                const size_t row = (size_t)(base + tt);
-                vv = v[row * ldv + (size_t)h * dv + jj];
-                if (v_scale != nullptr) vv *= v_scale[row * heads + h];
-            }
-            v_s[tt][cc] = vv;
+            const bool ok = tt < nt && jj < dv;
+            ls_cp_async_4(v_s(buf, tt) + cc, v + (size_t)(base + (ok ? tt : 0)) * ldv + (size_t)h * dv + (ok ? jj : 0), ok);
         }
+        if (threadIdx.x < TB) {
+            const int tt = threadIdx.x;
+            const bool ok = tt < nt;
+            const size_t row = (size_t)(base + (ok ? tt : 0));
+            if (!PER_CHANNEL) ls_cp_async_4(w_s(buf, tt), w + row * ldw + h, ok);
+            if (scaled) ls_cp_async_4(f_s(buf) + tt, v_scale + row * heads + h, ok);
+        }
+    };
+
+    // every turn commits one group, empty or not, so that "all but the last STAGES - 1 groups" is always this chunk
+    for (int st = 0; st < STAGES - 1; ++st) {
+        if (row0 + st * TB < row1) stage(st, row0 + st * TB);
+        asm volatile("cp.async.commit_group;\n" ::);
+    }
+    int buf = 0;
+    for (int base = row0; base < row1; base += TB, buf = (buf + 1 == STAGES ? 0 : buf + 1)) {
+        const int nt = min(TB, row1 - base);
+        const int ahead = base + (STAGES - 1) * TB;
+        if (ahead < row1) stage(buf == 0 ? STAGES - 1 : buf - 1, ahead);
+        asm volatile("cp.async.commit_group;\n" ::);
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 1));
         __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {
-            const float vv = v_s[tt][col];
-            float acc = 0.f;
+        float part[TB];     // this lane's share of each token's output
+        auto token = [&](int tt) {
+            const float vv = scaled ? v_s(buf, tt)[col] * f_s(buf)[tt] : v_s(buf, tt)[col];
+            const float wh = PER_CHANNEL ? 0.f : w_s(buf, tt)[0];
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < C; ++i) {
-                const float kv = k_s[tt][c0 + i] * vv;
-                if (with_bonus) {
-                    acc = fmaf(q_s[tt][c0 + i], fmaf(U[i], kv, S[i]), acc);
-                    S[i] = fmaf(w_s[tt][c0 + i], S[i], kv);
-                } else {
-                    S[i] = fmaf(w_s[tt][c0 + i], S[i], kv);
-                    acc = fmaf(q_s[tt][c0 + i], S[i], acc);
+            for (int i4 = 0; i4 < C / 4; ++i4) {
+                const int c4 = (i4 * LS_LANES + lane) * 4;
+                const float4 q4 = *reinterpret_cast<const float4*>(q_s(buf, tt) + c4);
+                const float4 k4 = *reinterpret_cast<const float4*>(k_s(buf, tt) + c4);
+                float4 w4 = make_float4(wh, wh, wh, wh);
+                if (PER_CHANNEL) w4 = *reinterpret_cast<const float4*>(w_s(buf, tt) + (PER_CHANNEL ? c4 : 0));
+                const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, ka[4] = {k4.x, k4.y, k4.z, k4.w}, wa[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = i4 * 4 + e;
+                    const float kv = ka[e] * vv;
+                    if (BONUS) {
+                        acc[e] = fmaf(qa[e], fmaf(U[i], kv, S[i]), acc[e]);
+                        S[i] = fmaf(wa[e], S[i], kv);
+                    } else {
+                        S[i] = fmaf(wa[e], S[i], kv);
+                        acc[e] = fmaf(qa[e], S[i], acc[e]);
+                    }
                 }
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            if (lane == 0 && j < dv) o[(size_t)(base + tt) * ldo + (size_t)h * dv + j] = acc;
+            return (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        };
+        if (nt == TB) {     // a full chunk, unrolled: only the state chains its tokens
+#pragma unroll
+            for (int tt = 0; tt < TB; ++tt) part[tt] = token(tt);
+        } else {
+#pragma unroll
+            for (int tt = 0; tt < TB; ++tt) part[tt] = tt < nt ? token(tt) : 0.f;
         }
+        // The eight lanes of a column sum their shares of the eight tokens in three exchanges (4 + 2 + 1 shuffles), each
+        // lane keeping half of what it held: lane l ends with token l's output. The pairs are those of a butterfly over
+        // one token's shares (lane ^ 4, then ^ 2, then ^ 1), whatever the chunk holds.
+        {
+            const bool up4 = (lane & 4) != 0, up2 = (lane & 2) != 0, up1 = (lane & 1) != 0;
+            float h4[4], h2[2];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float recv = __shfl_xor_sync(0xffffffffu, up4 ? part[t] : part[t + 4], 4);
+                h4[t] = (up4 ? part[t + 4] : part[t]) + recv;
+            }
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const float recv = __shfl_xor_sync(0xffffffffu, up2 ? h4[t] : h4[t + 2], 2);
+                h2[t] = (up2 ? h4[t + 2] : h4[t]) + recv;
+            }
+            const float recv = __shfl_xor_sync(0xffffffffu, up1 ? h2[0] : h2[1], 1);
+            const float total = (up1 ? h2[1] : h2[0]) + recv;
+            if (lane < nt && j < dv) o[(size_t)(base + lane) * ldo + (size_t)h * dv + j] = total * q_scale;
+        }
+        __syncthreads();        // the chunk has been walked: its buffer may be filled again
     }
     if (j < dv) {
 #pragma unroll
-        for (int i = 0; i < C; ++i)
-            if (c0 + i < dk) srow[c0 + i] = S[i];
+        for (int i = 0; i < C; ++i) {
+            const int c = ((i >> 2) * LS_LANES + lane) * 4 + (i & 3);
+            if (c < dk) srow[c] = S[i];
+        }
     }
 }
 
@@ -111,14 +188,31 @@ NIB_API int nib_linear_state_scan(const float* q, int ldq, const float* k, int l
     NIB_REQUIRE(dk > 0 && dk <= 256 && dv > 0, "linear_state_scan: key size %d is outside 1..256", dk);
     if (n_req <= 0) return 0;
     const dim3 grid(ceil_div(dv, LS_COLS), heads, n_req), block(LS_THREADS);
-#define NIB_LS_LAUNCH(C)                                                                                                     \
-    linear_state_scan_kernel<C><<<grid, block, 0, stream>>>(q, ldq, k, ldk, v, ldv, w, ldw, w_per_channel, bonus, v_scale, state, \
-                                                            state_ld, state_off, q_start, slots, o, ldo, heads, kq_heads, dk, dv, q_scale)
+#define NIB_LS_LAUNCH3(C, PC, B)                                                                                                    \
+    do {                                                                                                                            \
+        static bool configured = false;                                                                                             \
+        if (!configured) {                                                                                                          \
+            NIB_CUDA(cudaFuncSetAttribute(linear_state_scan_kernel<C, PC, B>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                                          LsLayout<C, PC>::BYTES));                                                                 \
+            configured = true;                                                                                                      \
+        }                                                                                                                           \
+        linear_state_scan_kernel<C, PC, B><<<grid, block, LsLayout<C, PC>::BYTES, stream>>>(                                        \
+            q, ldq, k, ldk, v, ldv, w, ldw, bonus, v_scale, state, state_ld, state_off, q_start, slots, o, ldo, heads, kq_heads,    \
+            dk, dv, q_scale);                                                                                                       \
+    } while (0)
+#define NIB_LS_LAUNCH(C)                                            \
+    do {                                                            \
+        if (w_per_channel && bonus != nullptr) NIB_LS_LAUNCH3(C, true, true);   \
+        else if (w_per_channel) NIB_LS_LAUNCH3(C, true, false);     \
+        else if (bonus != nullptr) NIB_LS_LAUNCH3(C, false, true);  \
+        else NIB_LS_LAUNCH3(C, false, false);                       \
+    } while (0)
     if (dk <= 32) NIB_LS_LAUNCH(4);
     else if (dk <= 64) NIB_LS_LAUNCH(8);
     else if (dk <= 128) NIB_LS_LAUNCH(16);
     else NIB_LS_LAUNCH(32);
 #undef NIB_LS_LAUNCH
+#undef NIB_LS_LAUNCH3
     NIB_LAUNCH_CHECK();
     return 0;
 }
@@ -185,6 +279,63 @@ NIB_API int nib_conv_tail(const float* x, int ldx, float* state, long long state
     if (n_req == 0 || taps == 1) return 0;
     NIB_CUDA(launch_pdl(conv_tail_kernel, dim3(ceil_div((long long)n_req * width, 256)), dim3(256), (size_t)0, stream, x, ldx, state, state_ld,
                         state_off, q_start, slots, n_req, width, taps));
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+// Both in one launch for steps of a few tokens per request (a decode step): one thread per (request, channel) walks the
+// request's tokens with the history in registers, then writes the history back. The same arithmetic per output as
+// conv_tokens_kernel (taps added in ascending order from the bias).
+constexpr int CONV_STEP_MAX_TAPS = 16;
+
+__global__ void __launch_bounds__(256)
+conv_step_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ bias, int act,
+                 float* __restrict__ state, long long state_ld, int state_off, const int* __restrict__ q_start,
+                 const int* __restrict__ slots, float* __restrict__ y, int ldy, int n_req, int width, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    const long long e = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (e >= (long long)n_req * width) return;
+    const int r = (int)(e / width), c = (int)(e % width);
+    const int first = q_start[r], len = q_start[r + 1] - first;
+    float* hist = taps > 1 ? state + (long long)slots[r] * state_ld + state_off : nullptr;
+    float win[CONV_STEP_MAX_TAPS - 1], wt[CONV_STEP_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < CONV_STEP_MAX_TAPS; ++j) {
+        wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+        if (j < CONV_STEP_MAX_TAPS - 1) win[j] = j < taps - 1 ? hist[(size_t)j * width + c] : 0.f;
+    }
+    const float b = bias != nullptr ? bias[c] : 0.f;
+    for (int i = 0; i < len; ++i) {
+        const float u = x[(size_t)(first + i) * ldx + c];
+        float acc = b;
+#pragma unroll
+        for (int j = 0; j < CONV_STEP_MAX_TAPS - 1; ++j)
+            if (j < taps - 1) acc = fmaf(wt[j], win[j], acc);
+#pragma unroll
+        for (int j = 0; j < CONV_STEP_MAX_TAPS; ++j)
+            if (j == taps - 1) acc = fmaf(wt[j], u, acc);
+        if (act == 1) acc = acc / (1.0f + expf(-acc));
+        y[(size_t)(first + i) * ldy + c] = acc;
+#pragma unroll
+        for (int j = 0; j < CONV_STEP_MAX_TAPS - 1; ++j) {
+            if (j < taps - 2) win[j] = win[j + 1 < CONV_STEP_MAX_TAPS - 1 ? j + 1 : j];
+            else if (j == taps - 2) win[j] = u;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < CONV_STEP_MAX_TAPS - 1; ++j)
+        if (j < taps - 1) hist[(size_t)j * width + c] = win[j];
+}
+
+NIB_API int nib_conv_step(const float* x, int ldx, const float* w, const float* bias, int act, float* state, long long state_ld,
+                          int state_off, const int* q_start, const int* slots, float* y, int ldy, int n_req, int width, int taps,
+                          cudaStream_t stream) {
+    NIB_REQUIRE(n_req >= 0 && width > 0 && taps >= 1 && taps <= CONV_STEP_MAX_TAPS && (taps == 1 || state != nullptr),
+                "conv_step: bad sizes, more than %d taps, or no state", CONV_STEP_MAX_TAPS);
+    if (n_req == 0) return 0;
+    NIB_CUDA(launch_pdl(conv_step_kernel, dim3(ceil_div((long long)n_req * width, 256)), dim3(256), (size_t)0, stream, x, ldx, w, bias, act,
+                        state, state_ld, state_off, q_start, slots, y, ldy, n_req, width, taps));
     NIB_LAUNCH_CHECK();
     return 0;
 }

@@ -127,9 +127,7 @@ class FlexAttention(Mixer):
         qkv32 = p32[:, :self.n_qkv]
         if self.taps:
             conv32 = torch.empty((m, self.n_qkv), dtype=torch.float32, device=dev)
-            ops.conv_tokens(qkv32, self.conv_w, None, "none", cache.state, 0, ctx, conv32, self.taps)
-            if self.taps > 1:
-                ops.conv_tail(qkv32, cache.state, 0, ctx, self.taps)
+            ops.conv_step(qkv32, self.conv_w, None, "none", cache.state, 0, ctx, conv32, self.taps)
             qkv32 = conv32
         q = torch.empty((m, self.nq), dtype=self.rt.dtype, device=dev)
         # norm, rotation, queries in the storage type, keys and values into their pages

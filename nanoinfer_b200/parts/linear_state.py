@@ -197,9 +197,7 @@ class Mamba2Mixer(Mixer):
         ops.linear(h, self.w_in, None, p32, "f32")
         xbc_in = p32[:, inner:2 * inner + 2 * gn]
         xbc = torch.empty((m, inner + 2 * gn), dtype=torch.float32, device=dev)
-        ops.conv_tokens(xbc_in, self.conv_w, self.conv_b, "silu", cache.state, 0, ctx, xbc, self.taps)
-        if self.taps > 1:
-            ops.conv_tail(xbc_in, cache.state, 0, ctx, self.taps)
+        ops.conv_step(xbc_in, self.conv_w, self.conv_b, "silu", cache.state, 0, ctx, xbc, self.taps)
         dt = torch.empty((m, self.heads), dtype=torch.float32, device=dev)
         decay = torch.empty((m, self.heads), dtype=torch.float32, device=dev)
         ops.step_sizes(p32[:, 2 * inner + 2 * gn:], self.dt_bias, self.a_log, dt, decay)

@@ -128,6 +128,17 @@ def test_short_convolution_in_steps_keeps_its_history(ops, width, taps, act):
         assert_close(out, ref, torch.float32, f"step {step}")
         assert_close(state, ref_state, torch.float32, f"state after step {step}")
     assert (state[:, :off] == 7.0).all() and (state[:, off + (taps - 1) * width:] == -7.0).all()
+    # both in one call: few tokens take one launch, many take two; the same bits either way
+    for q_lens in ([3, 1, 16], [40, 2]):
+        ctx, _, _ = batch(q_lens, [0] * len(q_lens), slots=[1, 3, 0][:len(q_lens)])
+        x = rnd(sum(q_lens), width, seed=30 + len(q_lens))
+        s_a, s_b = state.clone(), state.clone()
+        out_a, out_b = torch.empty(sum(q_lens), width, device=DEV), torch.empty(sum(q_lens), width, device=DEV)
+        ops.conv_step(x, w, bias, act, s_a, off, ctx, out_a, taps)
+        ops.conv_tokens(x, w, bias, act, s_b, off, ctx, out_b, taps)
+        if taps > 1:
+            ops.conv_tail(x, s_b, off, ctx, taps)
+        assert torch.equal(out_a, out_b) and torch.equal(s_a, s_b)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -238,6 +238,11 @@ class TorchOps:
             hist.copy_(padded[-(taps - 1):])
             start += q_len
 
+    def conv_step(self, x32, w32, bias32, act, state, state_off, ctx, out32, taps):
+        self.conv_tokens(x32, w32, bias32, act, state, state_off, ctx, out32, taps)
+        if taps > 1:
+            self.conv_tail(x32, state, state_off, ctx, taps)
+
     def token_shift(self, h, mu32, state, state_off, ctx, mixes):
         start = 0
         width = h.shape[1]
