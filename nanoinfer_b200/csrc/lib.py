@@ -708,12 +708,18 @@ class Kernels:
             raise KernelError(f"{what}: the state does not hold {size} floats from column {off}")
 
     def linear_state_scan(self, q32, k32, v32, w32, state, state_off, ctx, o32, heads, kq_heads, dk, dv, q_scale=1.0,
-                          bonus32=None, v_scale32=None):
+                          bonus32=None, v_scale32=None, seg_len=None):
         """Per request and head, over the step's tokens in order, from and into ``state[slot, state_off:]`` (laid out
         [head, value channel, key channel]): S <- diag(w) S + k (v_scale v)^T, o = S^T (q_scale q); with ``bonus32``
         [heads, dk] instead o = (S_old + diag(bonus) k v^T)^T q before the update. q32, k32: [tokens, kq_heads * dk]
         (head h reads key head h // (heads / kq_heads)); v32, o32: [tokens, heads * dv]; w32: [tokens, heads * dk] (a
-        decay per key channel) or [tokens, heads] (one per head); v_scale32: [tokens, heads]."""
+        decay per key channel) or [tokens, heads] (one per head); v_scale32: [tokens, heads].
+
+        A step in which a request brings 256 tokens or more, and whose walk in order would not fill the GPU, is walked in
+        segments of 128 tokens or more side by side (every
+        segment from a zero state, the end states chained with the products of the segments' decays, then every segment
+        again from its true entry state): the result then depends on the cut by rounding. ``seg_len``: None = that rule,
+        0 = never, another multiple of 8 = segments of that length whenever a request brings more."""
         for t, what, width in ((q32, "q", kq_heads * dk), (k32, "k", kq_heads * dk), (v32, "v", heads * dv), (o32, "o", heads * dv)):
             self._rows(t, torch.float32, f"linear_state_scan {what}")
             if tuple(t.shape) != (q32.shape[0], width):
@@ -731,11 +737,27 @@ class Kernels:
             if tuple(v_scale32.shape) != (q32.shape[0], heads):
                 raise KernelError("linear_state_scan: v_scale does not fit")
         self._state_row(state, state_off, heads * dv * dk, "linear_state_scan state")
+        n_req, longest = ctx.host.num_requests, max(ctx.host.q_lens)
+        if seg_len is None:
+            # segments pay (the work doubles) while the walk in order leaves SMs idle or with one warp per scheduler:
+            # as many segments as bring the blocks to about eight per SM, none shorter than 128 tokens
+            want = (8 * max(1, self.sm_count)) // max(1, -(-dv // 16) * heads * n_req)
+            seg_len = max(128, -(-(-(-longest // want)) // 8) * 8) if longest >= 256 and want >= 2 else 0
+        n_seg = -(-longest // seg_len) if seg_len and longest > seg_len else 1
+        scratch = None
+        if n_seg > 1:
+            floats = n_req * n_seg * heads * (dv * dk + dk)
+            if floats * 4 > (1 << 29):      # half a gigabyte of entry states: walk in order instead
+                n_seg = 1
+            else:
+                scratch = torch.empty(floats, dtype=torch.float32, device=q32.device)
+                self.launches += 2
         self._check(self._lib.nib_linear_state_scan(
             _ptr(q32), c_int(q32.stride(0)), _ptr(k32), c_int(k32.stride(0)), _ptr(v32), c_int(v32.stride(0)), _ptr(w32),
             c_int(w32.stride(0)), c_int(1 if per_channel else 0), _ptr(bonus32), _ptr(v_scale32), _ptr(state), c_longlong(state.stride(0)),
             c_int(state_off), _ptr(ctx.q_start), _ptr(ctx.state_slots), _ptr(o32), c_int(o32.stride(0)), c_int(ctx.host.num_requests),
-            c_int(heads), c_int(kq_heads), c_int(dk), c_int(dv), c_float(q_scale), self._stream()), "linear_state_scan")
+            c_int(heads), c_int(kq_heads), c_int(dk), c_int(dv), c_float(q_scale), c_int(n_seg), c_int(seg_len if n_seg > 1 else 0), _ptr(scratch),
+            self._stream()), "linear_state_scan")
 
     def conv_tokens(self, x32, w32, bias32, act, state, state_off, ctx, out32, taps):
         """out32[t, c] = act(bias32[c] + sum_j w32[c, j] * x32[t - (taps-1-j), c]) within each request; inputs before the

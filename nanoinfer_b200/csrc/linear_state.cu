@@ -46,13 +46,19 @@ template <int C, bool PER_CHANNEL> struct LsLayout {
     static constexpr int BYTES = STAGES * STAGE * 4;
 };
 
-template <int C, bool PER_CHANNEL, bool BONUS>
+// MODE 0: a request's tokens from its slot's state to its slot's state. For long prompts the tokens are cut into
+// segments of seg_len that run side by side: MODE 1 walks every segment but a request's last from a zero state (no
+// outputs) and leaves its end state and the product of its decays; ls_combine_kernel chains them into every segment's
+// true entry state; MODE 2 walks every segment again from that state with outputs, the last one into the slot.
+// seg_state: [request, segment, head, value channel, key channel]; seg_decay: [request, segment, head, key channel or 1].
+template <int C, bool PER_CHANNEL, bool BONUS, int MODE>
 __global__ void __launch_bounds__(LS_THREADS)
 linear_state_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk, const float* __restrict__ v, int ldv,
                          const float* __restrict__ w, int ldw, const float* __restrict__ bonus,
                          const float* __restrict__ v_scale, float* __restrict__ state, long long state_ld, int state_off,
                          const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ o, int ldo,
-                         int heads, int kq_heads, int dk, int dv, float q_scale) {
+                         int heads, int kq_heads, int dk, int dv, float q_scale, int n_seg, int seg_len,
+                         float* __restrict__ seg_state, float* __restrict__ seg_decay) {
     using L = LsLayout<C, PER_CHANNEL>;
     constexpr int DKP = L::DKP, TB = L::TB, STAGES = L::STAGES;
     extern __shared__ __align__(16) float ls_smem[];
@@ -61,18 +67,28 @@ linear_state_scan_kernel(const float* __restrict__ q, int ldq, const float* __re
     auto w_s = [&](int buf, int tt) { return ls_smem + buf * L::STAGE + L::W0 + tt * L::WP; };
     auto v_s = [&](int buf, int tt) { return ls_smem + buf * L::STAGE + L::V0 + tt * LS_COLS; };
     auto f_s = [&](int buf) { return ls_smem + buf * L::STAGE + L::F0; };
-    const int req = blockIdx.z, h = blockIdx.y;
+    const int req = MODE == 0 ? blockIdx.z : blockIdx.z / n_seg, seg = MODE == 0 ? 0 : blockIdx.z % n_seg, h = blockIdx.y;
     const int hq = h / (heads / kq_heads);
     const int lane = threadIdx.x & (LS_LANES - 1), col = threadIdx.x / LS_LANES;
     const int j = blockIdx.x * LS_COLS + col;
-    const int row0 = q_start[req], row1 = q_start[req + 1];
+    const int req_row1 = q_start[req + 1];
+    const int row0 = q_start[req] + (MODE == 0 ? 0 : seg * seg_len);
+    const int row1 = MODE == 0 ? req_row1 : min(req_row1, row0 + seg_len);
+    if (row0 >= req_row1) return;                       // the request has fewer segments
+    const bool last = row1 == req_row1;
+    if (MODE == 1 && last) return;                      // a request's last segment ends in the slot, in the second walk
     float* srow = state + (long long)slots[req] * state_ld + state_off + ((long long)h * dv + j) * dk;
-    float S[C], U[C];
+    const size_t elems = (size_t)heads * dv * dk;
+    float* seg_row = MODE == 0 ? nullptr : seg_state + ((size_t)req * n_seg + seg) * elems + ((size_t)h * dv + j) * dk;
+    const bool track = MODE == 1 && blockIdx.x == 0 && col == 0;       // these eight lanes also multiply the segment's decays up
+    float S[C], U[C], P[MODE == 1 ? C : 1];
 #pragma unroll
     for (int i = 0; i < C; ++i) {
         const int c = ((i >> 2) * LS_LANES + lane) * 4 + (i & 3);
-        S[i] = (j < dv && c < dk) ? srow[c] : 0.f;
+        const float* from = MODE == 2 ? seg_row : srow;
+        S[i] = (MODE != 1 && j < dv && c < dk) ? from[c] : 0.f;
         U[i] = (BONUS && c < dk) ? bonus[(size_t)h * dk + c] : 0.f;
+        if (MODE == 1) P[i] = 1.f;
     }
     const bool scaled = v_scale != nullptr;
 
@@ -83,7 +99,7 @@ linear_state_scan_kernel(const float* __restrict__ q, int ldq, const float* __re
             const bool ok = tt < nt && c < dk;
             const size_t row = (size_t)(base + (ok ? tt : 0));
             const int cc = ok ? c : 0;
-            ls_cp_async_4(q_s(buf, tt) + c, q + row * ldq + (size_t)hq * dk + cc, ok);
+            if (MODE != 1) ls_cp_async_4(q_s(buf, tt) + c, q + row * ldq + (size_t)hq * dk + cc, ok);
             ls_cp_async_4(k_s(buf, tt) + c, k + row * ldk + (size_t)hq * dk + cc, ok);
             if (PER_CHANNEL) ls_cp_async_4(w_s(buf, tt) + c, w + row * ldw + (size_t)h * dk + cc, ok);
         }
@@ -122,7 +138,8 @@ linear_state_scan_kernel(const float* __restrict__ q, int ldq, const float* __re
 #pragma unroll
             for (int i4 = 0; i4 < C / 4; ++i4) {
                 const int c4 = (i4 * LS_LANES + lane) * 4;
-                const float4 q4 = *reinterpret_cast<const float4*>(q_s(buf, tt) + c4);
+                float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (MODE != 1) q4 = *reinterpret_cast<const float4*>(q_s(buf, tt) + c4);
                 const float4 k4 = *reinterpret_cast<const float4*>(k_s(buf, tt) + c4);
                 float4 w4 = make_float4(wh, wh, wh, wh);
                 if (PER_CHANNEL) w4 = *reinterpret_cast<const float4*>(w_s(buf, tt) + (PER_CHANNEL ? c4 : 0));
@@ -131,7 +148,10 @@ linear_state_scan_kernel(const float* __restrict__ q, int ldq, const float* __re
                 for (int e = 0; e < 4; ++e) {
                     const int i = i4 * 4 + e;
                     const float kv = ka[e] * vv;
-                    if (BONUS) {
+                    if (MODE == 1) {
+                        S[i] = fmaf(wa[e], S[i], kv);
+                        if (track) P[i] *= wa[e];
+                    } else if (BONUS) {
                         acc[e] = fmaf(qa[e], fmaf(U[i], kv, S[i]), acc[e]);
                         S[i] = fmaf(wa[e], S[i], kv);
                     } else {
@@ -152,7 +172,7 @@ linear_state_scan_kernel(const float* __restrict__ q, int ldq, const float* __re
         // The eight lanes of a column sum their shares of the eight tokens in three exchanges (4 + 2 + 1 shuffles), each
         // lane keeping half of what it held: lane l ends with token l's output. The pairs are those of a butterfly over
         // one token's shares (lane ^ 4, then ^ 2, then ^ 1), whatever the chunk holds.
-        {
+        if (MODE != 1) {
             const bool up4 = (lane & 4) != 0, up2 = (lane & 2) != 0, up1 = (lane & 1) != 0;
             float h4[4], h2[2];
 #pragma unroll
@@ -171,34 +191,97 @@ linear_state_scan_kernel(const float* __restrict__ q, int ldq, const float* __re
         }
         __syncthreads();        // the chunk has been walked: its buffer may be filled again
     }
-    if (j < dv) {
+    float* to = MODE == 0 ? srow : (MODE == 1 ? seg_row + elems : (last ? srow : nullptr));     // a segment's end is the next one's entry
+    if (j < dv && to != nullptr) {
 #pragma unroll
         for (int i = 0; i < C; ++i) {
             const int c = ((i >> 2) * LS_LANES + lane) * 4 + (i & 3);
-            if (c < dk) srow[c] = S[i];
+            if (c < dk) to[c] = S[i];
+        }
+    }
+    if (MODE == 1 && track) {
+        float* pd = seg_decay + (((size_t)req * n_seg + seg) * heads + h) * (PER_CHANNEL ? dk : 1);
+        if (PER_CHANNEL) {
+#pragma unroll
+            for (int i = 0; i < C; ++i) {
+                const int c = ((i >> 2) * LS_LANES + lane) * 4 + (i & 3);
+                if (c < dk) pd[c] = P[MODE == 1 ? i : 0];
+            }
+        } else if (lane == 0) {
+            pd[0] = P[0];
         }
     }
 }
 
+// Entry states of a request's segments: seg_state[0] = the slot's state, seg_state[s + 1] = decay(s) * seg_state[s] +
+// (what the first walk left there: segment s walked from zero). One thread per state element.
+__global__ void __launch_bounds__(256)
+ls_combine_kernel(const float* __restrict__ state, long long state_ld, int state_off, const int* __restrict__ q_start,
+                  const int* __restrict__ slots, float* __restrict__ seg_state, const float* __restrict__ seg_decay, int n_req,
+                  int n_seg, int seg_len, int heads, int dk, int dv, int per_channel) {
+    const size_t elems = (size_t)heads * dv * dk;
+    const long long e = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (e >= (long long)n_req * elems) return;
+    const int req = (int)(e / elems);
+    const size_t x = (size_t)(e % elems);
+    const int c = (int)(x % dk), h = (int)(x / ((size_t)dv * dk));
+    const int len = q_start[req + 1] - q_start[req];
+    const int segs = (len + seg_len - 1) / seg_len;
+    float S = state[(long long)slots[req] * state_ld + state_off + x];
+    float* base = seg_state + (size_t)req * n_seg * elems + x;
+    base[0] = S;
+    for (int s = 0; s + 1 < segs; ++s) {
+        const float p = per_channel ? seg_decay[(((size_t)req * n_seg + s) * heads + h) * dk + c] : seg_decay[((size_t)req * n_seg + s) * heads + h];
+        S = fmaf(p, S, base[(size_t)(s + 1) * elems]);
+        base[(size_t)(s + 1) * elems] = S;
+    }
+}
+
+// The number of floats of scratch that the walk in segments wants for these sizes (states, then decay products).
+NIB_API long long nib_linear_state_scan_scratch(int n_req, int n_seg, int heads, int dk, int dv) {
+    return (long long)n_req * n_seg * heads * ((long long)dv * dk + dk);
+}
+
+// n_seg <= 1: every request's tokens in order, one block per (request, head, 16 value columns). n_seg > 1 (long
+// prompts): segments of seg_len tokens side by side (see the kernel); scratch holds nib_linear_state_scan_scratch floats.
 NIB_API int nib_linear_state_scan(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* w, int ldw,
                                   int w_per_channel, const float* bonus, const float* v_scale, float* state, long long state_ld,
                                   int state_off, const int* q_start, const int* slots, float* o, int ldo, int n_req, int heads,
-                                  int kq_heads, int dk, int dv, float q_scale, cudaStream_t stream) {
+                                  int kq_heads, int dk, int dv, float q_scale, int n_seg, int seg_len, float* scratch,
+                                  cudaStream_t stream) {
     NIB_REQUIRE(heads > 0 && kq_heads > 0 && heads % kq_heads == 0, "linear_state_scan: %d heads do not share %d key heads", heads, kq_heads);
     NIB_REQUIRE(dk > 0 && dk <= 256 && dv > 0, "linear_state_scan: key size %d is outside 1..256", dk);
+    NIB_REQUIRE(n_seg <= 1 || (scratch != nullptr && seg_len > 0 && seg_len % 8 == 0), "linear_state_scan: segments need scratch and a length that is a multiple of 8");
     if (n_req <= 0) return 0;
-    const dim3 grid(ceil_div(dv, LS_COLS), heads, n_req), block(LS_THREADS);
-#define NIB_LS_LAUNCH3(C, PC, B)                                                                                                    \
+    const bool cut = n_seg > 1;
+    float* seg_state = scratch;
+    float* seg_decay = cut ? scratch + (size_t)n_req * n_seg * heads * dv * dk : nullptr;
+    const dim3 block(LS_THREADS);
+#define NIB_LS_LAUNCH4(C, PC, B, MODE)                                                                                              \
     do {                                                                                                                            \
         static bool configured = false;                                                                                             \
         if (!configured) {                                                                                                          \
-            NIB_CUDA(cudaFuncSetAttribute(linear_state_scan_kernel<C, PC, B>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+            NIB_CUDA(cudaFuncSetAttribute(linear_state_scan_kernel<C, PC, B, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
                                           LsLayout<C, PC>::BYTES));                                                                 \
             configured = true;                                                                                                      \
         }                                                                                                                           \
-        linear_state_scan_kernel<C, PC, B><<<grid, block, LsLayout<C, PC>::BYTES, stream>>>(                                        \
+        const dim3 grid(ceil_div(dv, LS_COLS), heads, n_req * (MODE == 0 ? 1 : n_seg));                                             \
+        linear_state_scan_kernel<C, PC, B, MODE><<<grid, block, LsLayout<C, PC>::BYTES, stream>>>(                                  \
             q, ldq, k, ldk, v, ldv, w, ldw, bonus, v_scale, state, state_ld, state_off, q_start, slots, o, ldo, heads, kq_heads,    \
-            dk, dv, q_scale);                                                                                                       \
+            dk, dv, q_scale, n_seg, seg_len, seg_state, seg_decay);                                                                 \
+        NIB_LAUNCH_CHECK();                                                                                                         \
+    } while (0)
+#define NIB_LS_LAUNCH3(C, PC, B)                                                                                                    \
+    do {                                                                                                                            \
+        if (!cut) {                                                                                                                 \
+            NIB_LS_LAUNCH4(C, PC, B, 0);                                                                                            \
+        } else {                                                                                                                    \
+            NIB_LS_LAUNCH4(C, PC, false, 1);                                                                                        \
+            ls_combine_kernel<<<ceil_div((long long)n_req * heads * dv * dk, 256), 256, 0, stream>>>(                               \
+                state, state_ld, state_off, q_start, slots, seg_state, seg_decay, n_req, n_seg, seg_len, heads, dk, dv, PC ? 1 : 0); \
+            NIB_LAUNCH_CHECK();                                                                                                     \
+            NIB_LS_LAUNCH4(C, PC, B, 2);                                                                                            \
+        }                                                                                                                           \
     } while (0)
 #define NIB_LS_LAUNCH(C)                                            \
     do {                                                            \
@@ -213,7 +296,7 @@ NIB_API int nib_linear_state_scan(const float* q, int ldq, const float* k, int l
     else NIB_LS_LAUNCH(32);
 #undef NIB_LS_LAUNCH
 #undef NIB_LS_LAUNCH3
-    NIB_LAUNCH_CHECK();
+#undef NIB_LS_LAUNCH4
     return 0;
 }
 

@@ -208,6 +208,33 @@ def test_walk_against_plain_and_cut_anywhere(ops, heads, kq_heads, dk, dv, mode)
     assert torch.equal(state2[0], state[1])
 
 
+@pytest.mark.parametrize("heads,kq_heads,dk,dv,mode", [(2, 2, 20, 12, "bonus"), (4, 2, 48, 40, "scalar"), (2, 2, 64, 64, "post"), (1, 1, 130, 70, "bonus")])
+def test_long_prompts_walked_in_segments(ops, heads, kq_heads, dk, dv, mode):
+    """A prompt of 700 tokens beside a short request and a decoded token: segments side by side give what the walk in
+    order gives, up to rounding; the states go on from there (a second step in order)."""
+    q_lens, slots, off = [700, 3, 1], [2, 0, 1], 7
+    m, size = sum(q_lens), heads * dv * dk
+    q, k, v, w = _walk_inputs(m, heads, kq_heads, dk, dv, 3, mode == "scalar")
+    bonus = rnd(heads, dk, seed=7) if mode == "bonus" else None
+    v_scale = torch.rand(m, heads, generator=torch.Generator().manual_seed(8)).to(DEV) if mode == "scalar" else None
+    ctx, _, _ = batch(q_lens, [0, 0, 0], slots=slots)
+    start = rnd(3, off + size + 2, seed=9, scale=0.3)          # the requests do not start from zero
+    outs, states = [], []
+    for seg_len in (0, None, 64):
+        state, out = start.clone(), torch.empty(m, heads * dv, device=DEV)
+        ops.linear_state_scan(q, k, v, w, state, off, ctx, out, heads, kq_heads, dk, dv, bonus32=bonus, v_scale32=v_scale, seg_len=seg_len)
+        outs.append(out); states.append(state)
+    ref_state, ref = start.cpu().clone(), torch.empty(m, heads * dv)
+    TorchOps().linear_state_scan(q.cpu(), k.cpu(), v.cpu(), w.cpu(), ref_state, off, to_cpu(ctx), ref, heads, kq_heads, dk, dv,
+                                 bonus32=None if bonus is None else bonus.cpu(), v_scale32=None if v_scale is None else v_scale.cpu())
+    for out, state, what in zip(outs, states, ("in order", "segments of 128", "segments of 64")):
+        assert_close(out, ref, torch.float32, what)
+        assert_close(state, ref_state, torch.float32, what + ": state")
+        assert torch.equal(state[:, :off], start[:, :off]) and torch.equal(state[:, off + size:], start[:, off + size:])
+    assert torch.equal(outs[0][700:], outs[1][700:])            # the short requests are walked in order either way
+    assert not torch.equal(outs[0][:700], outs[1][:700]) or dk == 1
+
+
 def test_walk_remembers_a_far_key(ops):
     """One token writes a value under a key no other token uses; 600 tokens later a query for that key still finds it,
     scaled by the product of the decays in between."""

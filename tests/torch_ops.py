@@ -269,7 +269,7 @@ class TorchOps:
         decay_out.copy_(torch.exp(-torch.exp(a_log32.double()) * dt_out.double()).to(torch.float32))
 
     def linear_state_scan(self, q32, k32, v32, w32, state, state_off, ctx, o32, heads, kq_heads, dk, dv, q_scale=1.0,
-                          bonus32=None, v_scale32=None):
+                          bonus32=None, v_scale32=None, seg_len=None):
         start = 0
         rep = heads // kq_heads
         per_channel = w32.shape[1] == heads * dk
