@@ -100,18 +100,29 @@ attention_flex_mma_kernel(const __nv_bfloat16* __restrict__ q_in, int q_stride, 
                           const int* __restrict__ block_table, int bt_stride, int page_size,
                           const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages, int num_pages,
                           int heads, int kv_heads, int dk, int dv, float scale, float softcap, const float* __restrict__ slopes,
-                          int window, int chunk, float out_scale) {
+                          int window, int chunk, float out_scale, int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int req = blockIdx.y, kvh = blockIdx.z;
     const int n_rep = heads / kv_heads;
     const int row_begin = q_start[req], q_len = q_start[req + 1] - row_begin;
     const int rows_total = q_len * n_rep;
-    const int row0 = blockIdx.x * (FWARPS * 16);
+    // splits > 1 (steps of a few tokens per request: all rows fit one tile): blockIdx.x is a share of the key tiles
+    const int split = splits > 1 ? blockIdx.x : 0;
+    const int row0 = splits > 1 ? 0 : blockIdx.x * (FWARPS * 16);
     if (row0 >= rows_total) return;
     const int ctx = ctx_lens[req];
-    if (ctx <= 0) return;                             // a padding row of a replayed step
-    const int pos0 = ctx - q_len;                     // position of the request's first token in this step
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2;
+    if (ctx <= 0) {                                   // a padding row of a replayed step: shares that hold nothing
+        if (splits > 1)
+            for (int row = tid; row < rows_total; row += FWARPS * 32) {
+                const int ti = row / n_rep, head = kvh * n_rep + (row - ti * n_rep);
+                const size_t slot = ((size_t)(row_begin + ti) * heads + head) * splits + split;
+                part_ml[slot * 2] = -INFINITY;
+                part_ml[slot * 2 + 1] = 0.f;
+            }
+        return;
+    }
+    const int pos0 = ctx - q_len;                     // position of the request's first token in this step
     const int* bt = block_table + (size_t)req * bt_stride;
 
     auto first_visible = [&](int p) {
@@ -142,7 +153,12 @@ attention_flex_mma_kernel(const __nv_bfloat16* __restrict__ q_in, int q_stride, 
     const int last_row = min(rows_total, row0 + FWARPS * 16) - 1;
     const int hi_cta = pos0 + last_row / n_rep;
     const int lo_cta = first_visible(pos0 + row0 / n_rep);
-    const int t_begin = lo_cta / FB_N, t_end = hi_cta / FB_N;
+    int t_begin = lo_cta / FB_N, t_end = hi_cta / FB_N;
+    if (splits > 1) {       // this CTA's share of the tiles; it may be empty
+        const int per = (t_end - t_begin + splits) / splits;
+        t_begin += split * per;
+        t_end = min(t_end, t_begin + per - 1);
+    }
 
     pdl_wait();     // queries, and the keys and values of this step's tokens, come from the kernels before
     unsigned q[DKP / 16][4];
@@ -171,8 +187,10 @@ attention_flex_mma_kernel(const __nv_bfloat16* __restrict__ q_in, int q_stride, 
     unsigned char* k_buf[2] = {smem, smem + FxTile<DKP>::BYTES};
     unsigned char* v_buf[2] = {smem + 2 * FxTile<DKP>::BYTES, smem + 2 * FxTile<DKP>::BYTES + FxTile<DVP>::BYTES};
 
-    fx_load_tile<DKP>(k_buf[0], k_pages, dk, bt, page_size, num_pages, kv_heads, kvh, t_begin * FB_N, lo_cta, hi_cta, tid);
-    fx_load_tile<DVP>(v_buf[0], v_pages, dv, bt, page_size, num_pages, kv_heads, kvh, t_begin * FB_N, lo_cta, hi_cta, tid);
+    if (t_begin <= t_end) {
+        fx_load_tile<DKP>(k_buf[0], k_pages, dk, bt, page_size, num_pages, kv_heads, kvh, t_begin * FB_N, lo_cta, hi_cta, tid);
+        fx_load_tile<DVP>(v_buf[0], v_pages, dv, bt, page_size, num_pages, kv_heads, kvh, t_begin * FB_N, lo_cta, hi_cta, tid);
+    }
     fx_commit();
 
     for (int tile = t_begin; tile <= t_end; ++tile) {
@@ -213,6 +231,18 @@ attention_flex_mma_kernel(const __nv_bfloat16* __restrict__ q_in, int q_stride, 
     pdl_launch_dependents();
 
     const int t = lane & 3;
+    if (splits > 1) {       // sums, maxima (base-2 units) and unnormalized outputs of this share; a second kernel merges them
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            if (out_off[r] < 0) continue;
+            const size_t slot = (size_t)(out_off[r] / dv) * splits + split;        // (token * heads + head) * splits + split
+            if (t == 0) { part_ml[slot * 2] = m_run[r]; part_ml[slot * 2 + 1] = l_run[r]; }
+#pragma unroll
+            for (int d = 0; d < DVP / 8; ++d)
+                if (d * 8 < dv) *reinterpret_cast<float2*>(part_o + slot * dv + d * 8 + 2 * t) = make_float2(o[d][2 * r], o[d][2 * r + 1]);
+        }
+        return;
+    }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         if (out_off[r] < 0) continue;
@@ -224,10 +254,36 @@ attention_flex_mma_kernel(const __nv_bfloat16* __restrict__ q_in, int q_stride, 
     }
 }
 
+// Merges the shares of one (token, head), in share order: a block of 128 threads per row of part_o.
+template <typename TO>
+__global__ void __launch_bounds__(128)
+attention_flex_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, TO* __restrict__ out, int splits, int dv,
+                            float out_scale) {
+    pdl_wait();
+    const size_t row = blockIdx.x;
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(row * splits + s) * 2]);
+    float l = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float ms = part_ml[(row * splits + s) * 2];
+        if (ms != -INFINITY) l += part_ml[(row * splits + s) * 2 + 1] * exp2f(ms - m);
+    }
+    const float inv = l > 0.f ? out_scale / l : 0.f;
+    for (int d = threadIdx.x; d < dv; d += 128) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = part_ml[(row * splits + s) * 2];
+            if (ms != -INFINITY) acc += part_o[(row * splits + s) * dv + d] * exp2f(ms - m);
+        }
+        Elem<TO>::store(out + row * dv + d, acc * inv);
+    }
+}
+
 template <int DKP, int DVP, typename TO>
 int fx_launch(const void* q, int q_stride, void* out, const int* q_start, const int* ctx_lens, const int* block_table, int bt_stride,
               int page_size, const void* k_pages, const void* v_pages, int num_pages, int n_req, int max_q_len, int heads, int kv_heads,
-              int dk, int dv, float scale, float softcap, const float* slopes, int window, int chunk, float out_scale, cudaStream_t stream) {
+              int dk, int dv, float scale, float softcap, const float* slopes, int window, int chunk, float out_scale, int splits,
+              float* part_o, float* part_ml, int m_tokens, cudaStream_t stream) {
     static bool configured = false;
     const int smem = 2 * FxTile<DKP>::BYTES + 2 * FxTile<DVP>::BYTES;
     if (!configured) {
@@ -235,10 +291,14 @@ int fx_launch(const void* q, int q_stride, void* out, const int* q_start, const 
         configured = true;
     }
     const int n_rep = heads / kv_heads;
-    dim3 grid(ceil_div((long long)max_q_len * n_rep, FWARPS * 16), n_req, kv_heads);
+    dim3 grid(splits > 1 ? splits : ceil_div((long long)max_q_len * n_rep, FWARPS * 16), n_req, kv_heads);
     NIB_CUDA(launch_pdl(attention_flex_mma_kernel<DKP, DVP, TO>, grid, dim3(FWARPS * 32), (size_t)smem, stream, (const __nv_bfloat16*)q, q_stride,
                         (TO*)out, q_start, ctx_lens, block_table, bt_stride, page_size, (const __nv_bfloat16*)k_pages,
-                        (const __nv_bfloat16*)v_pages, num_pages, heads, kv_heads, dk, dv, scale, softcap, slopes, window, chunk, out_scale));
+                        (const __nv_bfloat16*)v_pages, num_pages, heads, kv_heads, dk, dv, scale, softcap, slopes, window, chunk, out_scale,
+                        splits, part_o, part_ml));
+    if (splits > 1)
+        NIB_CUDA(launch_pdl(attention_flex_merge_kernel<TO>, dim3(m_tokens * heads), dim3(128), (size_t)0, stream, (const float*)part_o,
+                            (const float*)part_ml, (TO*)out, splits, dv, out_scale));
     return 0;
 }
 
@@ -250,23 +310,28 @@ NIB_API int nib_attention_flex_mma_supported(int heads, int kv_heads, int dk, in
 }
 
 // q: rows of q_stride bfloat16 whose first heads*dk are the prepared queries; out: [tokens, heads*dv] floats (out_f32)
-// or bfloat16; q_start [n_req + 1], ctx_lens [n_req]; max_q_len: the most tokens a request brings.
+// or bfloat16; q_start [n_req + 1], ctx_lens [n_req]; max_q_len: the most tokens a request brings. splits > 1: the key
+// tiles of every request are shared out to that many CTAs (part_o: [m_tokens * heads * splits * dv] floats, part_ml:
+// [m_tokens * heads * splits * 2]) and a second kernel merges the shares.
 NIB_API int nib_attention_flex_mma(const void* q, int q_stride, void* out, int out_f32, const int* q_start, const int* ctx_lens,
                                    const int* block_table, int bt_stride, int page_size, const void* k_pages, const void* v_pages,
                                    int num_pages, int n_req, int max_q_len, int heads, int kv_heads, int dk, int dv, float scale,
-                                   float softcap, const float* slopes, int window, int chunk, float out_scale, cudaStream_t stream) {
+                                   float softcap, const float* slopes, int window, int chunk, float out_scale, int splits, float* part_o,
+                                   float* part_ml, int m_tokens, cudaStream_t stream) {
     NIB_REQUIRE(nib_attention_flex_mma_supported(heads, kv_heads, dk, dv, q_stride) == 1, "attention (tensor cores): head sizes %d / %d or head counts %d / %d are not taken", dk, dv, heads, kv_heads);
     NIB_REQUIRE(n_req >= 0 && max_q_len > 0 && page_size > 0 && num_pages > 0 && window >= 0 && chunk >= 0 && softcap >= 0.f, "attention (tensor cores): bad sizes");
+    NIB_REQUIRE(splits <= 1 || (max_q_len * (heads / kv_heads) <= 64 && part_o != nullptr && part_ml != nullptr),
+                "attention (tensor cores): keys are split over CTAs only when a request's rows fit one tile, and with scratch");
     if (n_req == 0) return 0;
 #define NIB_FXM(DKP, DVP)                                                                                                                   \
     do {                                                                                                                                    \
         const int rc = out_f32 ? fx_launch<DKP, DVP, float>(q, q_stride, out, q_start, ctx_lens, block_table, bt_stride, page_size, k_pages, \
                                                             v_pages, num_pages, n_req, max_q_len, heads, kv_heads, dk, dv, scale, softcap,   \
-                                                            slopes, window, chunk, out_scale, stream)                                        \
+                                                            slopes, window, chunk, out_scale, splits, part_o, part_ml, m_tokens, stream)      \
                                    : fx_launch<DKP, DVP, __nv_bfloat16>(q, q_stride, out, q_start, ctx_lens, block_table, bt_stride,         \
                                                                         page_size, k_pages, v_pages, num_pages, n_req, max_q_len, heads,     \
                                                                         kv_heads, dk, dv, scale, softcap, slopes, window, chunk, out_scale,  \
-                                                                        stream);                                                             \
+                                                                        splits, part_o, part_ml, m_tokens, stream);                          \
         if (rc != 0) return rc;                                                                                                             \
     } while (0)
     if (dk <= 64 && dv <= 64) NIB_FXM(64, 64);

@@ -688,8 +688,8 @@ class Kernels:
             if t is not None:
                 _need(t, torch.float32, f"gated_norm {what}")
         norm = 1 if groups else 0
-        if not groups:      # no norm: any split of the row will do; parts of up to 256 channels keep the warps short
-            groups = next(g for g in range(max(1, n // 256), 0, -1) if n % g == 0)
+        if not groups:      # no norm: any split of the row will do; parts of about 128 channels keep the warps short
+            groups = next((g for g in range(max(1, n // 128), n + 1) if n % g == 0), 1)
         if gain32 is not None and gain32.numel() not in (n, n // groups):
             raise KernelError("gated_norm: the gain has neither a row's size nor a part's")
         self._check(self._lib.nib_gated_norm(
@@ -890,11 +890,25 @@ class Kernels:
         if q.dtype == torch.bfloat16 and not self.options.force_general_attention and page_size > 0 \
                 and self._lib.nib_attention_flex_mma_supported(c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(q.stride(0))) == 1:
             # bfloat16 heads of up to 128 (multiples of 8): tensor cores, prompt portions and decoded tokens alike
+            longest, splits, part_o, part_ml = max(ctx.host.q_lens), 1, None, None
+            if longest * (heads // kv_heads) <= 64:
+                # a step of few tokens per request (decoding): a CTA that walks a long context alone waits for memory
+                # tile after tile; two tiles per CTA are both in flight at once
+                keys = max(ctx.host.ctx_lens)
+                for bound in (window, chunk):
+                    keys = min(keys, bound) if bound > 0 else keys
+                most = max(1, (4 * max(1, self.sm_count)) // max(1, ctx.host.num_requests * kv_heads))
+                splits = self.options.fixed_decode_splits or max(1, min(-(-(keys // 64 + 1) // 2), most, 32))
+                if splits > 1:
+                    part_o = torch.empty(m * heads * splits * vdim, dtype=torch.float32, device=q.device)
+                    part_ml = torch.empty(m * heads * splits * 2, dtype=torch.float32, device=q.device)
+                    self.launches += 1
             self._check(self._lib.nib_attention_flex_mma(
                 _ptr(q), c_int(q.stride(0)), _ptr(out), c_int(1 if out.dtype == torch.float32 else 0), _ptr(ctx.q_start), _ptr(ctx.ctx_lens),
                 _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(k_pages.shape[0]),
                 c_int(ctx.host.num_requests), c_int(max(ctx.host.q_lens)), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_float(scale),
-                c_float(softcap), _ptr(slopes32), c_int(window), c_int(chunk), c_float(out_scale), self._stream()), "attention (options, tensor cores)")
+                c_float(softcap), _ptr(slopes32), c_int(window), c_int(chunk), c_float(out_scale), c_int(splits), _ptr(part_o), _ptr(part_ml),
+                c_int(m), self._stream()), "attention (options, tensor cores)")
             return
         self._check(self._lib.nib_attention_flex(
             _ptr(q), c_int(q.stride(0)), _ptr(out), c_int(1 if out.dtype == torch.float32 else 0), _ptr(ctx.positions), _ptr(ctx.req_index),

@@ -451,6 +451,47 @@ gated_norm_kernel(const float* __restrict__ o, int ldo, const float* __restrict_
     }
 }
 
+// The same for wide parts (a state-space mixer's norm over thousands of channels): a block of 256 threads per
+// (token, part), so that the few rows of a decode step are not walked by one warp each.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_norm_block_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ gate, int ldg, int gate_kind, int gate_first,
+                        const float* __restrict__ gain, int gain_len, const float* __restrict__ skip, int lds,
+                        const float* __restrict__ coef, int coef_span, int norm, float eps, float out_scale,
+                        T* __restrict__ out, int ld_out, int tokens, int groups, int width) {
+    pdl_launch_dependents();
+    pdl_wait();      // everything this kernel reads may come from the kernel before
+    __shared__ float part[8];
+    const int t = blockIdx.x / groups, c0 = (blockIdx.x % groups) * width;
+    const float* orow = o + (size_t)t * ldo;
+    const float* grow = gate != nullptr ? gate + (size_t)t * ldg : nullptr;
+    const float* srow = skip != nullptr ? skip + (size_t)t * lds : nullptr;
+    const bool early = grow != nullptr && gate_kind != 0 && gate_first != 0;
+    const bool late = grow != nullptr && gate_kind != 0 && gate_first == 0;
+    float scale = 1.0f;
+    if (norm) {
+        float ss = 0.f;
+        for (int j = threadIdx.x; j < width; j += 256) {
+            const int c = c0 + j;
+            float y = orow[c];
+            if (srow != nullptr) y = fmaf(coef[c / coef_span], srow[c], y);
+            if (early) y *= gate_act(grow[c], gate_kind);
+            ss = fmaf(y, y, ss);
+        }
+        scale = 1.0f / sqrtf(block_sum_256(ss, part) / (float)width + eps);
+    }
+    for (int j = threadIdx.x; j < width; j += 256) {
+        const int c = c0 + j;
+        float y = orow[c];
+        if (srow != nullptr) y = fmaf(coef[c / coef_span], srow[c], y);
+        if (early) y *= gate_act(grow[c], gate_kind);
+        y *= scale;
+        if (gain != nullptr) y *= gain[c % gain_len];
+        if (late) y *= gate_act(grow[c], gate_kind);
+        Elem<T>::store(out + (size_t)t * ld_out + c, y * out_scale);
+    }
+}
+
 NIB_API int nib_gated_norm(const float* o, int ldo, const float* gate, int ldg, int gate_kind, int gate_first, const float* gain,
                            int gain_len, const float* skip, int lds, const float* coef, int n_coef, int groups, int norm, float eps,
                            float out_scale, void* out, int ld_out, int tokens, int n, int dtype, cudaStream_t stream) {
@@ -460,6 +501,14 @@ NIB_API int nib_gated_norm(const float* o, int ldo, const float* gate, int ldg, 
     NIB_REQUIRE(gate_kind >= 0 && gate_kind <= 2, "gated_norm: unknown gate kind %d", gate_kind);
     if (tokens == 0) return 0;
     const int width = n / groups, span = skip != nullptr ? n / n_coef : 1;
+    if (width > 256) {
+        const dim3 grid(tokens * groups);
+        if (dtype == NIB_F32) NIB_CUDA(launch_pdl(gated_norm_block_kernel<float>, grid, dim3(256), (size_t)(0), stream, o, ldo, gate, ldg, gate_kind, gate_first, gain, gain_len, skip, lds, coef, span, norm, eps, out_scale, (float*)out, ld_out, tokens, groups, width));
+        else if (dtype == NIB_BF16) NIB_CUDA(launch_pdl(gated_norm_block_kernel<__nv_bfloat16>, grid, dim3(256), (size_t)(0), stream, o, ldo, gate, ldg, gate_kind, gate_first, gain, gain_len, skip, lds, coef, span, norm, eps, out_scale, (__nv_bfloat16*)out, ld_out, tokens, groups, width));
+        else NIB_REQUIRE(false, "gated_norm: unknown dtype %d", dtype);
+        NIB_LAUNCH_CHECK();
+        return 0;
+    }
     const int blocks = ceil_div((long long)tokens * groups, 4);
     if (dtype == NIB_F32) NIB_CUDA(launch_pdl(gated_norm_kernel<float>, dim3(blocks), dim3(128), (size_t)(0), stream, o, ldo, gate, ldg, gate_kind, gate_first, gain, gain_len, skip, lds, coef, span, norm, eps, out_scale, (float*)out, ld_out, tokens, groups, width));
     else if (dtype == NIB_BF16) NIB_CUDA(launch_pdl(gated_norm_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), (size_t)(0), stream, o, ldo, gate, ldg, gate_kind, gate_first, gain, gain_len, skip, lds, coef, span, norm, eps, out_scale, (__nv_bfloat16*)out, ld_out, tokens, groups, width));

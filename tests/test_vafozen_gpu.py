@@ -59,9 +59,9 @@ def rnd(*shape, seed=0, scale=1.0):
 
 # ------------------------------------------------------------------------------------------ pointwise kernels
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m,heads,d", [(5, 3, 20), (3, 4, 300)])        # narrow parts: a warp each; wide parts: a block each
 @pytest.mark.parametrize("case", ["head_norm_shared_gain_silu", "gate_first_skip_groups", "gate_only", "norm_only_full_gain"])
-def test_gate_norm_and_skip(ops, dtype, case):
-    m, heads, d = 5, 3, 20
+def test_gate_norm_and_skip(ops, dtype, case, m, heads, d):
     n = heads * d
     wide = rnd(m, 3 * n + 7, seed=1, scale=1.5)
     o, gate, skip = wide[:, 1:1 + n], wide[:, n + 3:2 * n + 3], wide[:, 2 * n + 5:3 * n + 5]        # rows lie apart
@@ -307,6 +307,17 @@ def test_attention_over_pages_with_options(ops, dtype, opts, heads, kv, dk, dv, 
     TorchOps().attention_flex(q.cpu(), ref, *args[:6], None if slopes is None else slopes.cpu(), *args[7:], 0.8, to_cpu(ctx), full_bt.cpu(),
                               page, kp.cpu(), vp.cpu())
     paths = [ops] if dtype == torch.float32 else [ops, ops.with_options(force_general_attention=True)]      # tensor cores; the general kernel
+    if dtype == torch.bfloat16:       # decoded tokens alone: their keys are shared out to several CTAs and merged
+        dq, dbefore = [1, 1, 1], [150, 6, 129]
+        dctx, _, _ = batch(dq, dbefore, page_size=page)
+        drows = torch.tensor([full_ctx.q_start[i].item() + b for i, b in enumerate(dbefore)], device=DEV)
+        dref = torch.empty(3, heads * dv, dtype=torch.float64)
+        TorchOps().attention_flex(q_all[drows].cpu(), dref, *args[:6], None if slopes is None else slopes.cpu(), *args[7:], 0.8, to_cpu(dctx),
+                                  full_bt.cpu(), page, kp.cpu(), vp.cpu())
+        for k in (ops, ops.with_options(fixed_decode_splits=5)):
+            out = torch.empty(3, heads * dv, dtype=dtype, device=DEV)
+            k.attention_flex(q_all[drows].contiguous(), out, *args, 0.8, dctx, full_bt, page, kp, vp)
+            assert_close(out, dref, dtype, f"{opts} decoded tokens, splits fixed {k is not ops}")
     for k in paths:
         for out_dtype in {torch.float32, dtype}:
             out = torch.empty(sum(q_lens), heads * dv, dtype=out_dtype, device=DEV)
