@@ -152,7 +152,7 @@ def random_config(rng):
             else:
                 rot = rng.choice([d for d in (2, 4, 8, 16, 32, dim) if d <= dim and d % 2 == 0])
                 left = softmax_half(heads, kv, dim, vdim, scale=rng.choice([None, 0.2]), conv=rng.choice([1, 2, 3, 4, 6]),
-                                    rot=(rot, rng.choice([100.0, 10000.0, 250000.0])), softcap=rng.choice([2.0, 20.0, 50.0]))
+                                    rot=(rot, rng.choice([100.0, 10000.0, 1e6])), softcap=rng.choice([2.0, 15.0, 50.0]))
                 layer = pair2(left, rh, rd, vdim=rv, rank=rng.choice([1, 4, 8, 16]), left_scale=rng.choice([0.5, 1.0]),
                               right_scale=rng.choice([0.9, 1.3]))
         layers.append(with_mlp(layer, ff))
