@@ -36,6 +36,12 @@ __device__ __forceinline__ void ls_cp_async_4(void* smem, const void* gmem, bool
 // One staged chunk in shared memory: TB tokens' q and k (DKP floats each), decays (DKP, or one per token), the block's
 // value columns and the factor on the values. STAGES chunks are in flight: a chunk's loads have the walk of the
 // STAGES - 1 chunks before it to arrive.
+__device__ __forceinline__ void ls_cp_async_16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+
 template <int C, bool PER_CHANNEL> struct LsLayout {
     static constexpr int DKP = LS_LANES * C;
     static constexpr int TB = 8;                        // as many tokens as lanes share a column: see the butterfly below
@@ -58,7 +64,7 @@ linear_state_scan_kernel(const float* __restrict__ q, int ldq, const float* __re
                          const float* __restrict__ v_scale, float* __restrict__ state, long long state_ld, int state_off,
                          const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ o, int ldo,
                          int heads, int kq_heads, int dk, int dv, float q_scale, int n_seg, int seg_len,
-                         float* __restrict__ seg_state, float* __restrict__ seg_decay) {
+                         float* __restrict__ seg_state, float* __restrict__ seg_decay, int vec) {
     using L = LsLayout<C, PER_CHANNEL>;
     constexpr int DKP = L::DKP, TB = L::TB, STAGES = L::STAGES;
     extern __shared__ __align__(16) float ls_smem[];
@@ -94,6 +100,17 @@ linear_state_scan_kernel(const float* __restrict__ q, int ldq, const float* __re
 
     auto stage = [&](int buf, int base) {
         const int nt = min(TB, row1 - base);
+        if (vec) {      // rows of q, k and decays start on 16-byte boundaries and dk is a multiple of 4: four floats a copy
+            for (int e = threadIdx.x; e < TB * (DKP / 4); e += LS_THREADS) {
+                const int tt = e / (DKP / 4), c = (e % (DKP / 4)) * 4;
+                const bool ok = tt < nt && c < dk;
+                const size_t row = (size_t)(base + (ok ? tt : 0));
+                const int cc = ok ? c : 0;
+                if (MODE != 1) ls_cp_async_16(q_s(buf, tt) + c, q + row * ldq + (size_t)hq * dk + cc, ok);
+                ls_cp_async_16(k_s(buf, tt) + c, k + row * ldk + (size_t)hq * dk + cc, ok);
+                if (PER_CHANNEL) ls_cp_async_16(w_s(buf, tt) + c, w + row * ldw + (size_t)h * dk + cc, ok);
+            }
+        } else
         for (int e = threadIdx.x; e < TB * DKP; e += LS_THREADS) {
             const int tt = e / DKP, c = e % DKP;
             const bool ok = tt < nt && c < dk;
@@ -254,6 +271,8 @@ NIB_API int nib_linear_state_scan(const float* q, int ldq, const float* k, int l
     NIB_REQUIRE(n_seg <= 1 || (scratch != nullptr && seg_len > 0 && seg_len % 8 == 0), "linear_state_scan: segments need scratch and a length that is a multiple of 8");
     if (n_req <= 0) return 0;
     const bool cut = n_seg > 1;
+    auto aligned = [](const void* p, int ld) { return ((uintptr_t)p & 15) == 0 && ld % 4 == 0; };
+    const int vec = (dk % 4 == 0 && aligned(q, ldq) && aligned(k, ldk) && (!w_per_channel || aligned(w, ldw))) ? 1 : 0;
     float* seg_state = scratch;
     float* seg_decay = cut ? scratch + (size_t)n_req * n_seg * heads * dv * dk : nullptr;
     const dim3 block(LS_THREADS);
@@ -268,7 +287,7 @@ NIB_API int nib_linear_state_scan(const float* q, int ldq, const float* k, int l
         const dim3 grid(ceil_div(dv, LS_COLS), heads, n_req * (MODE == 0 ? 1 : n_seg));                                             \
         linear_state_scan_kernel<C, PC, B, MODE><<<grid, block, LsLayout<C, PC>::BYTES, stream>>>(                                  \
             q, ldq, k, ldk, v, ldv, w, ldw, bonus, v_scale, state, state_ld, state_off, q_start, slots, o, ldo, heads, kq_heads,    \
-            dk, dv, q_scale, n_seg, seg_len, seg_state, seg_decay);                                                                 \
+            dk, dv, q_scale, n_seg, seg_len, seg_state, seg_decay, vec);                                                            \
         NIB_LAUNCH_CHECK();                                                                                                         \
     } while (0)
 #define NIB_LS_LAUNCH3(C, PC, B)                                                                                                    \
