@@ -108,7 +108,8 @@ attention_flex_mma_kernel(const __nv_bfloat16* __restrict__ q_in, int q_stride, 
     const int rows_total = q_len * n_rep;
     // splits > 1 (steps of a few tokens per request: all rows fit one tile): blockIdx.x is a share of the key tiles
     const int split = splits > 1 ? blockIdx.x : 0;
-    const int row0 = splits > 1 ? 0 : blockIdx.x * (FWARPS * 16);
+    // the last row tiles of a prompt see the most keys: they start first, so that the kernel does not end on its longest CTA
+    const int row0 = splits > 1 ? 0 : (gridDim.x - 1 - blockIdx.x) * (FWARPS * 16);
     if (row0 >= rows_total) return;
     const int ctx = ctx_lens[req];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2;
@@ -217,7 +218,9 @@ attention_flex_mma_kernel(const __nv_bfloat16* __restrict__ q_in, int q_stride, 
                     const int r = e >> 1;
                     const int key = tile * FB_N + n * 8 + 2 * t + (e & 1);
                     float x = s[n][e] * scale;
-                    if (softcap > 0.f) x = softcap * tanhf(x * inv_cap);
+                    // tanh(y) = 1 - 2 / (1 + e^(2y)) with the fast exponential and division: off by a few 1e-7 in absolute
+                    // terms, far below the rounding of the probabilities to bfloat16 that follows
+                    if (softcap > 0.f) x = softcap * (1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x * inv_cap)));
                     s[n][e] = fmaf(x, LOG2E, -slope2[r] * (float)(vis_hi[r] - key));
                 }
             }
