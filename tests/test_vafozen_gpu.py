@@ -615,3 +615,35 @@ def test_trace_replay_as_a_child_process(folders, tmp_path):
     got1 = torch.from_numpy(np.fromfile(os.path.join(tmp_path, "1.f32"), dtype="<f4").reshape(2, -1))
     assert_close(got0, ref[[10]], torch.float32, "step 0")
     assert_close(got1, ref[[11, 19]], torch.float32, "step 1")
+
+
+def test_command_line_tools_generate_and_serve(folders):
+    """bin/generate (with the cache and recomputing every token) and bin/serve as child processes, in 32-bit: the plain
+    implementation's greedy tokens."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def tool(name, argv):
+        done = subprocess.run([sys.executable, os.path.join(root, "bin", name)] + argv, capture_output=True, text=True, timeout=600)
+        assert done.returncode == 0, done.stderr[-2000:]
+        return [[int(t) for t in line.split("Completion: ", 1)[1].split()] for line in done.stdout.splitlines()
+                if line.startswith("Completion: ")]
+
+    def greedy(prompt, n):
+        ids = list(prompt)
+        for _ in range(n):
+            ids.append(int(plain_logits(folders["B"], ids)[-1].argmax()))
+        return ids[len(prompt):]
+
+    prompts = [tokens(9, 77, 41), tokens(26, 77, 42)]
+    common = ["--model-dir", folders["B"], "--dtype", "float32", "--block-size", "8", "--num-blocks", "32", "--max-tokens", "6"]
+    for extra in ([], ["--no-cache"]):
+        (got,) = tool("generate", common + ["--prompt", " ".join(map(str, prompts[0]))] + extra)
+        assert got == greedy(prompts[0], 6), extra
+    argv = common + ["--max-batch", "2", "--max-tokens-per-step", "16"]
+    for p in prompts:
+        argv += ["--prompt", " ".join(map(str, p))]
+    got = tool("serve", argv)
+    assert got == [greedy(p, 6) for p in prompts]
